@@ -124,7 +124,7 @@ def add_replay_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens that live requests hold at any time (each rounded up to a multiple of 64)")
     p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    p.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    p.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
 
 
 def cmd_replay(args) -> int:

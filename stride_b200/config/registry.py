@@ -45,9 +45,9 @@ def config_class_for(name: str) -> type:
 
 
 def config_class_of(d: dict) -> type:
-    """Chooses the class by ``architectures`` (first registered name wins); a config.json that names none is
-    placed by its ``model_type``."""
-    names = d.get("architectures") or []
+    """Chooses the class by ``architectures`` (first registered name wins; the singular ``architecture`` with one
+    name is read the same way); a config.json that names none is placed by its ``model_type``."""
+    names = d.get("architectures") or d.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     if not names and d.get("model_type") in _MODEL_TYPES:

@@ -80,13 +80,35 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class StreamInputSpec:
+    """Something a layer adds to the residual stream from the token ids and the stream itself, after its
+    feed-forward. kind ``token_side``: a slice [offset, offset + dim) of row ``id`` of a second embedding table
+    (``table_name`` [vocab, table_width]) gated by a projection of the stream, projected back to ``hidden`` and
+    normed to unit root mean square with a plain weight."""
+    kind: str
+    hidden: int
+    vocab: int = 0
+    dim: int = 0
+    offset: int = 0
+    table_width: int = 0
+    table_name: str = ""
+    eps: float = 0.0
+    prefix: str = ""
+    params: tuple = ()
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """kind ``pre_norm``: x += mixer(norm(x)); x += ffn(norm(x))."""
+    """kind ``pre_norm``: x += m * mixer(norm(x)); x += m * ffn(norm(x)); then every part of ``after`` adds
+    m * part(x, tokens). ``residual_mult`` is m (1 where an architecture has none); ``feed_forward`` and
+    ``ffn_norm`` may be None for a layer without a feed-forward."""
     kind: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
+    residual_mult: float = 1.0
+    after: tuple = ()           # of StreamInputSpec
 
 
 @dataclass(frozen=True)

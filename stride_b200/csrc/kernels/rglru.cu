@@ -1,0 +1,201 @@
+// Recurrent block with a real-gated linear recurrent unit (the recurrent layer of Griffin: De et al., "Griffin:
+// Mixing Gated Linear Recurrences with Local Attention for Efficient Language Models").
+//
+// Per token, from the two projections of the layer's input (y~ and x~, both [width], in one matrix `xy`):
+//   x  = x~ + bias_x ;  u = conv_b + sum_j conv[c, j] * x(t - (taps - 1) + j)         causal, per channel
+//   r  = sigmoid(Wa[b] u_b + ba) ; i = sigmoid(Wi[b] u_b + bi)                        per block b of width / blocks channels
+//   a  = exp(-decay * r * softplus(lam)) ;  S_t = a S_(t-1) + sqrt(1 - a^2) * i * u   S in float32, zero at the start
+//   out = S_t * gelu_tanh(y~ + bias_y)
+// Everything after the projections is float32. Per request the state slot holds taps rows of [width] float32: rows
+// 0 .. taps-2 are the last taps-1 inputs x (oldest first; zero before the sequence starts, which is what a fresh slot
+// holds), row taps-1 is S. Three kernels, run in this order on any mix of portions and single tokens:
+//   rglru_conv    u for every token (reads the tail of the state, writes nothing to it)
+//   rglru_gates   the block-diagonal products with a and the gated input in the epilogue
+//   rglru_scan    the recurrence over each request's tokens, the output, and the new state (S and the tail)
+#include "common.cuh"
+
+namespace stride {
+
+constexpr int kMaxTaps = 16;
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rglru_conv_kernel(const T* __restrict__ xy, int ld, int x_off, const float* __restrict__ bias_x, const T* __restrict__ conv_w,
+                  const float* __restrict__ conv_b, const float* __restrict__ state, const int32_t* __restrict__ seq_of_token,
+                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ state_slot, float* __restrict__ u, int width,
+                  int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int seq = seq_of_token[t];
+    if (seq < 0) {
+        u[static_cast<size_t>(t) * width + c] = 0.f;
+        return;
+    }
+    const int start = q_start[seq];
+    const int local = t - start;
+    const float* tail = state + static_cast<size_t>(state_slot[seq]) * taps * width;
+    float acc = conv_b[c];
+    for (int j = 0; j < taps; ++j) {
+        const int src = local - (taps - 1) + j;
+        const float v = src >= 0 ? to_f32(xy[static_cast<size_t>(start + src) * ld + x_off + c]) + bias_x[c]
+                                 : tail[static_cast<size_t>(taps - 1 + src) * width + c];
+        acc = fmaf(to_f32(conv_w[static_cast<size_t>(c) * taps + j]), v, acc);
+    }
+    u[static_cast<size_t>(t) * width + c] = acc;
+}
+
+// wa_t / wi_t: the gate matrices transposed per block, [blocks, in, out], so that threads of neighbouring output
+// channels read neighbouring addresses. One CTA: GT tokens x 128 output channels of one block.
+constexpr int GT = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rglru_gates_kernel(const float* __restrict__ u, const T* __restrict__ wa_t, const T* __restrict__ wi_t, const float* __restrict__ ba,
+                   const float* __restrict__ bi, const float* __restrict__ lam, float decay, float* __restrict__ a_out,
+                   float* __restrict__ gx_out, int tokens, int width, int bw) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float us[];       // [GT][bw]
+    const int b = blockIdx.y;
+    const int t0 = blockIdx.z * GT;
+    const int oc = blockIdx.x * 128 + threadIdx.x;      // output channel inside the block
+    for (int i = threadIdx.x; i < GT * bw; i += 128) {
+        const int tt = i / bw, k = i % bw;
+        us[i] = t0 + tt < tokens ? u[static_cast<size_t>(t0 + tt) * width + b * bw + k] : 0.f;
+    }
+    __syncthreads();
+    if (oc >= bw) return;
+    float accr[GT], acci[GT];
+#pragma unroll
+    for (int tt = 0; tt < GT; ++tt) accr[tt] = acci[tt] = 0.f;
+    const T* wa = wa_t + static_cast<size_t>(b) * bw * bw + oc;
+    const T* wi = wi_t + static_cast<size_t>(b) * bw * bw + oc;
+    for (int k = 0; k < bw; ++k) {
+        const float wr = to_f32(wa[static_cast<size_t>(k) * bw]), wg = to_f32(wi[static_cast<size_t>(k) * bw]);
+#pragma unroll
+        for (int tt = 0; tt < GT; ++tt) {
+            const float x = us[tt * bw + k];
+            accr[tt] = fmaf(wr, x, accr[tt]);
+            acci[tt] = fmaf(wg, x, acci[tt]);
+        }
+    }
+    const int c = b * bw + oc;
+    const float rate = decay * softplus_f(lam[c]);
+    const float br = ba[c], bg = bi[c];
+#pragma unroll
+    for (int tt = 0; tt < GT; ++tt) {
+        if (t0 + tt >= tokens) break;
+        const float r = sigmoid_f(accr[tt] + br), g = sigmoid_f(acci[tt] + bg);
+        const float log_a = -rate * r;
+        const size_t at = static_cast<size_t>(t0 + tt) * width + c;
+        a_out[at] = expf(log_a);
+        gx_out[at] = sqrtf(-expm1f(2.f * log_a)) * g * us[tt * bw + oc];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ gx, const T* __restrict__ xy, int ld, int x_off, int y_off,
+                  const float* __restrict__ bias_x, const float* __restrict__ bias_y, float* __restrict__ state,
+                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len, const int32_t* __restrict__ state_slot,
+                  T* __restrict__ out, int width, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.y;
+    const int n = q_len[seq];
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n <= 0 || c >= width) return;
+    const int start = q_start[seq];
+    float* rows = state + static_cast<size_t>(state_slot[seq]) * taps * width;
+    float s = rows[static_cast<size_t>(taps - 1) * width + c];
+    const float by = bias_y[c];
+    for (int i = 0; i < n; ++i) {
+        const size_t at = static_cast<size_t>(start + i) * width + c;
+        s = fmaf(a[at], s, gx[at]);
+        const float y = gelu_tanh_f(to_f32(xy[static_cast<size_t>(start + i) * ld + y_off + c]) + by);
+        out[at] = from_f32<T>(s * y);
+    }
+    rows[static_cast<size_t>(taps - 1) * width + c] = s;
+    // the last taps-1 inputs, oldest first: from this step's tokens where it has them, else from the old tail
+    float tail[kMaxTaps];
+    const float bx = bias_x[c];
+    for (int r = 0; r < taps - 1; ++r) {
+        const int src = n - (taps - 1) + r;
+        tail[r] = src >= 0 ? to_f32(xy[static_cast<size_t>(start + src) * ld + x_off + c]) + bx
+                           : rows[static_cast<size_t>(taps - 1 + src) * width + c];
+    }
+    for (int r = 0; r < taps - 1; ++r) rows[static_cast<size_t>(r) * width + c] = tail[r];
+}
+
+}  // namespace stride
+
+using namespace stride;
+
+extern "C" {
+
+int stride_rglru_conv(const void* xy, int ld, int x_off, const float* bias_x, const void* conv_w, const float* conv_b, const float* state,
+                      const int32_t* seq_of_token, const int32_t* q_start, const int32_t* state_slot, float* u, int tokens, int width,
+                      int taps, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0 || taps <= 0 || ld <= 0 || x_off < 0) return STRIDE_BAD_ARGUMENT;
+    if (taps > kMaxTaps) return STRIDE_UNSUPPORTED;
+    if (tokens == 0) return 0;
+    const dim3 grid(tokens, (width + 255) / 256);
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(rglru_conv_kernel<float>, grid, dim3(256), 0, stream, static_cast<const float*>(xy), ld, x_off, bias_x,
+                       static_cast<const float*>(conv_w), conv_b, state, seq_of_token, q_start, state_slot, u, width, taps);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(rglru_conv_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(xy), ld, x_off,
+                       bias_x, static_cast<const __nv_bfloat16*>(conv_w), conv_b, state, seq_of_token, q_start, state_slot, u, width, taps);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_rglru_gates(const float* u, const void* wa_t, const void* wi_t, const float* ba, const float* bi, const float* lam, float decay,
+                       float* a_out, float* gx_out, int tokens, int width, int blocks, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0 || blocks <= 0 || width % blocks) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    const int bw = width / blocks;
+    const size_t smem = static_cast<size_t>(GT) * bw * sizeof(float);
+    if (smem > 48 * 1024) return STRIDE_UNSUPPORTED;
+    const dim3 grid((bw + 127) / 128, blocks, (tokens + GT - 1) / GT);
+    if (grid.z > 65535 || grid.y > 65535) return STRIDE_UNSUPPORTED;
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(rglru_gates_kernel<float>, grid, dim3(128), smem, stream, u, static_cast<const float*>(wa_t),
+                       static_cast<const float*>(wi_t), ba, bi, lam, decay, a_out, gx_out, tokens, width, bw);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(rglru_gates_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, u, static_cast<const __nv_bfloat16*>(wa_t),
+                       static_cast<const __nv_bfloat16*>(wi_t), ba, bi, lam, decay, a_out, gx_out, tokens, width, bw);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_rglru_scan(const float* a, const float* gx, const void* xy, int ld, int x_off, int y_off, const float* bias_x,
+                      const float* bias_y, float* state, const int32_t* q_start, const int32_t* q_len, const int32_t* state_slot, void* out,
+                      int num_seqs, int width, int taps, int dtype, cudaStream_t stream) {
+    if (num_seqs < 0 || width <= 0 || taps <= 0 || num_seqs > 65535) return STRIDE_BAD_ARGUMENT;
+    if (taps > kMaxTaps) return STRIDE_UNSUPPORTED;
+    if (num_seqs == 0) return 0;
+    const dim3 grid((width + 127) / 128, num_seqs);
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(rglru_scan_kernel<float>, grid, dim3(128), 0, stream, a, gx, static_cast<const float*>(xy), ld, x_off, y_off, bias_x,
+                       bias_y, state, q_start, q_len, state_slot, static_cast<float*>(out), width, taps);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(rglru_scan_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a, gx, static_cast<const __nv_bfloat16*>(xy), ld, x_off,
+                       y_off, bias_x, bias_y, state, q_start, q_len, state_slot, static_cast<__nv_bfloat16*>(out), width, taps);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+}  // extern "C"

@@ -1,0 +1,82 @@
+// Per-layer token input: a slice of a second embedding, gated by the residual stream, added to the stream.
+//
+// For token t with id v and stream row x (float32 [hidden]):
+//   e = table[v, offset : offset + dim]
+//   g = gelu_tanh(W_gate x) * e                    W_gate [dim, hidden]
+//   y = W_proj g                                   W_proj [hidden, dim]
+//   x <- x + scale * y / sqrt(mean(y^2) + eps) * norm_w
+// All of it in float32 on the stream row itself (the matrices are read in their stored type). One CTA per token:
+// the row is staged in shared memory, warps share the dim dot products over the row, then every thread owns
+// columns of y. Padded tokens are left alone.
+#include "common.cuh"
+
+namespace stride {
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_side_kernel(float* __restrict__ residual, const int32_t* __restrict__ ids, const int32_t* __restrict__ seq_of_token,
+                  const T* __restrict__ table, int table_width, int offset, int vocab, const T* __restrict__ w_gate,
+                  const T* __restrict__ w_proj, const float* __restrict__ norm_w, int hidden, int dim, float eps, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float smem[];
+    float* xs = smem;                 // hidden: the row, later y
+    float* g = smem + hidden;         // dim
+    float* scratch = g + dim;         // 32
+    const int t = blockIdx.x;
+    if (seq_of_token && seq_of_token[t] < 0) return;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    float* row = residual + static_cast<size_t>(t) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = row[i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const T* e = table + static_cast<size_t>(id) * table_width + offset;
+    for (int d = warp; d < dim; d += nwarps) {
+        const T* w = w_gate + static_cast<size_t>(d) * hidden;
+        float acc = 0.f;
+        for (int i = lane; i < hidden; i += 32) acc = fmaf(xs[i], to_f32(w[i]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) g[d] = gelu_tanh(acc) * to_f32(e[d]);
+    }
+    __syncthreads();
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const T* w = w_proj + static_cast<size_t>(c) * dim;
+        float y = 0.f;
+        for (int d = 0; d < dim; ++d) y = fmaf(to_f32(w[d]), g[d], y);
+        xs[c] = y;                    // each thread rewrites only the columns it reads back below
+        sq = fmaf(y, y, sq);
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row[c] = __fmaf_rn(scale, xs[c] * inv * norm_w[c], row[c]);
+}
+
+}  // namespace stride
+
+using namespace stride;
+
+extern "C" int stride_token_side(float* residual, const int32_t* ids, const int32_t* seq_of_token, const void* table, int table_width,
+                                 int offset, int vocab, const void* w_gate, const void* w_proj, const float* norm_w, int tokens,
+                                 int hidden, int dim, float eps, float scale, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || hidden <= 0 || dim <= 0 || offset < 0 || offset + dim > table_width || vocab <= 0) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    const size_t smem = static_cast<size_t>(hidden + dim + 32) * sizeof(float);
+    if (smem > 48 * 1024) return STRIDE_UNSUPPORTED;
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(token_side_kernel<float>, dim3(tokens), dim3(256), smem, stream, residual, ids, seq_of_token,
+                       static_cast<const float*>(table), table_width, offset, vocab, static_cast<const float*>(w_gate),
+                       static_cast<const float*>(w_proj), norm_w, hidden, dim, eps, scale);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(token_side_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), smem, stream, residual, ids, seq_of_token,
+                       static_cast<const __nv_bfloat16*>(table), table_width, offset, vocab, static_cast<const __nv_bfloat16*>(w_gate),
+                       static_cast<const __nv_bfloat16*>(w_proj), norm_w, hidden, dim, eps, scale);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}

@@ -76,6 +76,30 @@ _SIGNATURES = {
                                                  c_void_p, c_void_p, c_longlong, c_void_p]),
     "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_longlong, c_void_p]),
+    "stride_add_dyt": ("dynamic_tanh", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_void_p]),
+    "stride_add_scaled": ("dynamic_tanh", [c_void_p, c_void_p, c_float, c_longlong, c_int, c_void_p]),
+    "stride_token_side": ("token_side", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "stride_latent_prepare": ("latent_attention", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                   c_void_p]),
+    "stride_head_gemm": ("latent_attention", [c_void_p, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_latent_attention": ("latent_attention", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                                     c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "stride_rglru_conv": ("rglru", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_rglru_gates": ("rglru", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                     c_int, c_int, c_void_p]),
+    "stride_rglru_scan": ("rglru", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_moe_route": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_moe_plan": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "stride_grouped_gemm": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p]),
+    "stride_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_relu_squared": ("moe", [c_void_p, c_longlong, c_int, c_void_p]),
 }
 
 
@@ -100,6 +124,12 @@ _CLASS_OF = {
     "stride_silu_mul": "silu * up", "stride_paged_attention_generic": "attention (exact kernel)",
     "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
     "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling", "stride_sample_ranked": "sampling",
+    "stride_add_dyt": "norm", "stride_add_scaled": "residual sum", "stride_token_side": "token side input",
+    "stride_latent_prepare": "latent norm + rotation + cache write", "stride_head_gemm": "per-head product",
+    "stride_latent_attention": "attention (latent, exact kernel)", "stride_rglru_conv": "recurrent block: convolution",
+    "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_moe_route": "router",
+    "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
+    "stride_relu_squared": "relu^2",
 }
 
 
@@ -261,6 +291,154 @@ def silu_mul(inp, out, block: int | None = None) -> None:
         raise KernelError("silu_mul wants [tokens, 2*inter] in and [tokens, inter] out of one element type")
     _check(_fn("stride_silu_mul")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, inter if block is None else int(block),
                                   _code(out.dtype), _stream()), "silu_mul")
+
+
+# ------------------------------------------------------------ Dynamic Tanh, scaled sums
+def add_dyt(residual, delta, scale: float, weight, bias, alpha: float, out, rows=None) -> None:
+    """``x = residual (+ scale * delta)``; writes x back to ``residual`` (unless ``rows`` selects source rows) and
+    ``tanh(alpha * x) * weight + bias`` to ``out``."""
+    num_rows, hidden = out.shape
+    if delta is not None and delta.dtype != out.dtype:
+        raise KernelError("delta and out must have the same element type")
+    _check(_fn("stride_add_dyt")(_dev(residual, "residual", torch.float32), _opt(delta, "delta"), float(scale),
+                                 _dev(weight, "weight", torch.float32), _dev(bias, "bias", torch.float32), float(alpha), _dev(out, "out"),
+                                 _opt(rows, "rows", torch.int32), num_rows, hidden, _code(out.dtype), _stream()), "add_dyt")
+
+
+def add_scaled(residual, delta, scale: float) -> None:
+    """``residual += scale * delta`` in float32."""
+    _check(_fn("stride_add_scaled")(_dev(residual, "residual", torch.float32), _dev(delta, "delta"), float(scale), delta.numel(),
+                                    _code(delta.dtype), _stream()), "add_scaled")
+
+
+def token_side(residual, ids, seq_of_token, table, offset: int, w_gate, w_proj, norm_w, eps: float, scale: float) -> None:
+    """``residual[t] += scale * unit_rms(w_proj (gelu_tanh(w_gate residual[t]) * table[ids[t], offset:offset+dim])) * norm_w``,
+    in float32 on the stream itself. ``w_gate`` [dim, hidden], ``w_proj`` [hidden, dim]."""
+    tokens, hidden = residual.shape
+    dim = w_gate.shape[0]
+    if w_gate.shape != (dim, hidden) or w_proj.shape != (hidden, dim) or table.dtype != w_gate.dtype or w_proj.dtype != w_gate.dtype:
+        raise KernelError("token_side: the matrices do not fit the stream")
+    _check(_fn("stride_token_side")(_dev(residual, "residual", torch.float32), _dev(ids, "ids", torch.int32),
+                                    _opt(seq_of_token, "seq_of_token", torch.int32), _dev(table, "table"), table.shape[1], int(offset),
+                                    table.shape[0], _dev(w_gate, "w_gate"), _dev(w_proj, "w_proj"), _dev(norm_w, "norm_w", torch.float32),
+                                    tokens, hidden, dim, float(eps), float(scale), _code(w_gate.dtype), _stream()), "token_side")
+
+
+# --------------------------------------------------------------- latent attention
+def latent_prepare(proj, q_off: int, kv_off: int, qa, positions, seq_of_token, slot_mapping, cos, sin, latent_w, eps: float,
+                   latent_pages, krot_pages, heads: int, dim: int, rot: int, rot_dims: int, rank: int) -> None:
+    """From the projections of a step (``proj`` [tokens, ld]: queries at ``q_off``, the latent projection at ``kv_off``
+    or ``kv_off`` < 0 for none): the rotated parts of the queries into ``qa`` [tokens, heads, rank + rot], and, when
+    there is a latent projection and ``slot_mapping``, the normed latent and the rotated key part into their pages."""
+    tokens = proj.shape[0]
+    if qa.shape != (tokens, heads * (rank + rot)) or qa.dtype != proj.dtype:
+        raise KernelError("latent_prepare: qa must be [tokens, heads * (rank + rot)] of the projections' type")
+    has_kv = kv_off >= 0
+    _check(_fn("stride_latent_prepare")(
+        _dev(proj, "proj"), proj.shape[1], int(q_off), int(kv_off), _dev(qa, "qa"), _dev(positions, "positions", torch.int32),
+        _dev(seq_of_token, "seq_of_token", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32), _dev(cos, "cos", torch.float32),
+        _dev(sin, "sin", torch.float32), _opt(latent_w if has_kv else None, "latent_w", torch.float32), float(eps),
+        _opt(latent_pages if has_kv else None, "latent_pages", proj.dtype), _opt(krot_pages if has_kv else None, "krot_pages", proj.dtype),
+        tokens, heads, dim, rot, rot_dims, rank, _code(proj.dtype), _stream()), "latent_prepare")
+
+
+def head_gemm(a, lda: int, a_head_stride: int, b, b_head_stride: int, b_k_stride: int, b_n_stride: int, c, ldc: int, c_head_stride: int,
+              rows: int, heads: int, n: int, k: int, gate=None, ldg: int = 0, gate_off: int = 0, a_off: int = 0) -> None:
+    """Per head h: ``c[t, h, :n] = a[t, a_off + h * a_head_stride : ... + k] @ B_h`` with
+    ``B_h[k, n] = b[h * b_head_stride + k * b_k_stride + n * b_n_stride]``, times ``sigmoid(gate[t * ldg + gate_off + h])``
+    when a gate is given. Float32 accumulation in a fixed order."""
+    if a.dtype != b.dtype or c.dtype != a.dtype or (gate is not None and gate.dtype != a.dtype):
+        raise KernelError("head_gemm: one element type for all operands")
+    item = a.element_size()
+    gate_ptr = None if gate is None else _dev(gate, "gate") + gate_off * item
+    _check(_fn("stride_head_gemm")(_dev(a, "a") + a_off * item, lda, a_head_stride, _dev(b, "b"), b_head_stride, b_k_stride, b_n_stride,
+                                   _dev(c, "c"), ldc, c_head_stride, gate_ptr, ldg, rows, heads, n, k, _code(a.dtype), _stream()),
+           "head_gemm")
+
+
+def latent_attention(qa, out, latent_pages, krot_pages, block_table, seq_of_token, positions, heads: int, rank: int, rot: int,
+                     page_size: int, scale: float) -> None:
+    """Causal attention of every token over its request's latent pages: ``qa`` [tokens, heads * (rank + rot)] holds the
+    folded and the rotated query parts, ``out`` [tokens, heads * rank] receives the weighted sums of the latents."""
+    tokens = out.shape[0]
+    if out.shape[1] != heads * rank or qa.shape != (tokens, heads * (rank + rot)):
+        raise KernelError("latent_attention: shapes do not agree")
+    _check(_fn("stride_latent_attention")(
+        _dev(qa, "qa"), _dev(out, "out", qa.dtype), _dev(latent_pages, "latent_pages", qa.dtype), _dev(krot_pages, "krot_pages", qa.dtype),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(positions, "positions", torch.int32), tokens, heads, rank, rot, page_size, float(scale), _code(qa.dtype), _stream()),
+        "latent_attention")
+
+
+# ---------------------------------------------------------------- recurrent block
+def rglru_conv(xy, x_off: int, bias_x, conv_w, conv_b, state, seq_of_token, q_start, state_slot, u) -> None:
+    tokens, width = u.shape
+    taps = conv_w.shape[1]
+    _check(_fn("stride_rglru_conv")(_dev(xy, "xy"), xy.shape[1], int(x_off), _dev(bias_x, "bias_x", torch.float32), _dev(conv_w, "conv_w", xy.dtype),
+                                    _dev(conv_b, "conv_b", torch.float32), _dev(state, "state", torch.float32),
+                                    _dev(seq_of_token, "seq_of_token", torch.int32), _dev(q_start, "q_start", torch.int32),
+                                    _dev(state_slot, "state_slot", torch.int32), _dev(u, "u", torch.float32), tokens, width, taps,
+                                    _code(xy.dtype), _stream()), "rglru_conv")
+
+
+def rglru_gates(u, wa_t, wi_t, ba, bi, lam, decay: float, a_out, gx_out, blocks: int) -> None:
+    """``wa_t`` / ``wi_t``: the gate matrices of every block transposed, [blocks, in, out]."""
+    tokens, width = u.shape
+    _check(_fn("stride_rglru_gates")(_dev(u, "u", torch.float32), _dev(wa_t, "wa_t"), _dev(wi_t, "wi_t", wa_t.dtype), _dev(ba, "ba", torch.float32),
+                                     _dev(bi, "bi", torch.float32), _dev(lam, "lam", torch.float32), float(decay),
+                                     _dev(a_out, "a", torch.float32), _dev(gx_out, "gx", torch.float32), tokens, width, blocks,
+                                     _code(wa_t.dtype), _stream()), "rglru_gates")
+
+
+def rglru_scan(a, gx, xy, x_off: int, y_off: int, bias_x, bias_y, state, q_start, q_len, state_slot, out, num_seqs: int, taps: int) -> None:
+    width = out.shape[1]
+    _check(_fn("stride_rglru_scan")(_dev(a, "a", torch.float32), _dev(gx, "gx", torch.float32), _dev(xy, "xy", out.dtype), xy.shape[1],
+                                    int(x_off), int(y_off), _dev(bias_x, "bias_x", torch.float32), _dev(bias_y, "bias_y", torch.float32),
+                                    _dev(state, "state", torch.float32), _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
+                                    _dev(state_slot, "state_slot", torch.int32), _dev(out, "out"), num_seqs, width, taps,
+                                    _code(out.dtype), _stream()), "rglru_scan")
+
+
+# ------------------------------------------------------------------ routed experts
+def moe_route(h, w_router, bias, seq_of_token, ids, weights) -> None:
+    tokens, hidden = h.shape
+    experts, top = w_router.shape[0], ids.shape[1]
+    _check(_fn("stride_moe_route")(_dev(h, "h"), _dev(w_router, "w_router", h.dtype), _opt(bias, "bias", torch.float32),
+                                   _opt(seq_of_token, "seq_of_token", torch.int32), _dev(ids, "ids", torch.int32),
+                                   _dev(weights, "weights", torch.float32), tokens, hidden, experts, top, _code(h.dtype), _stream()), "moe_route")
+
+
+def moe_plan(ids, experts: int, offsets, perm_token, row_of, rank_tmp) -> None:
+    tokens, top = ids.shape
+    _check(_fn("stride_moe_plan")(_dev(ids, "ids", torch.int32), tokens, top, experts, _dev(offsets, "offsets", torch.int32),
+                                  _dev(perm_token, "perm_token", torch.int32), _dev(row_of, "row_of", torch.int32),
+                                  _dev(rank_tmp, "rank_tmp", torch.int32), _stream()), "moe_plan")
+
+
+def grouped_gemm(a, row_map, w, offsets, c, max_rows: int, act: int = 0) -> None:
+    """For every expert e and row p in ``offsets[e] .. offsets[e+1]``: ``c[p] = act(a[row_map[p]] @ w[e].T)`` (``row_map`` None:
+    row p itself). ``w`` [experts, n, k]; ``act`` 1 squares the positive part."""
+    experts, n, k = w.shape
+    if a.dtype == torch.float32:
+        kind = 0
+    elif c.dtype == torch.bfloat16:
+        kind = 1
+    else:
+        kind = 2
+    _check(_fn("stride_grouped_gemm")(_dev(a, "a"), a.shape[1], _opt(row_map, "row_map", torch.int32), _dev(w, "w", a.dtype),
+                                      _dev(offsets, "offsets", torch.int32), experts, _dev(c, "c"), c.shape[1], int(max_rows), n, k, int(act),
+                                      kind, _stream()), "grouped_gemm")
+
+
+def moe_combine(y, row_of, weights, shared, out) -> None:
+    tokens, hidden = out.shape
+    _check(_fn("stride_moe_combine")(_dev(y, "y", torch.float32), _dev(row_of, "row_of", torch.int32), _dev(weights, "weights", torch.float32),
+                                     _opt(shared, "shared", out.dtype), _dev(out, "out"), tokens, hidden, row_of.shape[1], _code(out.dtype),
+                                     _stream()), "moe_combine")
+
+
+def relu_squared(x) -> None:
+    _check(_fn("stride_relu_squared")(_dev(x, "x"), x.numel(), _code(x.dtype), _stream()), "relu_squared")
 
 
 # ----------------------------------------------------------------------- matmul

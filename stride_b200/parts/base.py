@@ -15,6 +15,8 @@ Mixer         ``forward(x, ctx, cache) -> delta``: x is the normed input
 FeedForward   ``forward(x, ctx) -> delta``.
 PositionEncoding  used by a mixer: ``encode_and_store`` rotates queries and keys
               in place and writes keys and values into the pages.
+StreamInput   ``forward(stream, ctx, scale)``: adds ``scale`` times something made from the step's token ids and the
+              stream itself to the stream (a per-layer token input).
 Layer         ``forward(stream, ctx, cache)``: the arrangement of the above.
 Embedding     ``forward(ctx, out)``: fills the float32 residual rows [tokens, hidden]
               from ``ctx.token_ids``; ``table()`` is what a tied head may share.
@@ -34,7 +36,7 @@ import torch
 
 from ..weights import TensorDecl
 
-CATEGORIES = ("norm", "mixer", "feed_forward", "position", "layer", "embedding", "head")
+CATEGORIES = ("norm", "mixer", "feed_forward", "position", "layer", "embedding", "head", "stream_input")
 _PARTS: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -118,6 +120,10 @@ class Projection:
 
 
 class Norm(Part):
+    # True: ``apply`` takes ``scale`` and computes ``residual + scale * pending``. For a norm without it the
+    # residual stream applies a scaled sum itself before it calls the norm.
+    takes_scale = False
+
     def fold_inputs(self):
         """Optional. ``(weight, eps)`` if the norm is ``x * rsqrt(mean(x^2) + eps) * weight`` with a float32
         weight: the residual stream may then fold it into the products before and after it."""
@@ -165,6 +171,12 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamInput(Part):
+    def forward(self, stream, ctx, scale: float) -> None:
+        """``stream``: the step's ``ResidualStream``; the part reads ``stream.materialize()`` and adds to it."""
+        raise NotImplementedError
+
+
 class Layer(Part):
     mixer: Mixer
 
@@ -193,4 +205,4 @@ class Head(Part):
 
 
 __all__ = ["CATEGORIES", "Embedding", "Head", "register_part", "build_part", "registered_parts", "CacheRequest", "StateRequest", "Part", "Norm",
-           "PositionEncoding", "Mixer", "FeedForward", "Layer", "TensorDecl", "Projection"]
+           "PositionEncoding", "Mixer", "FeedForward", "Layer", "StreamInput", "TensorDecl", "Projection"]

@@ -1,6 +1,8 @@
 """Arrangement of parts in a layer. ``pre_norm``: the mixer and the feed-forward
 each read a normed copy of the residual stream and add their output back
-(python/stride_worker/model.py:254-310)."""
+(python/stride_worker/model.py:254-310). The spec may put a multiplier on every
+sum into the stream, leave the feed-forward out, and name parts that add a
+token-dependent input to the stream after the feed-forward."""
 
 from __future__ import annotations
 
@@ -12,11 +14,15 @@ class PreNormLayer(Layer):
         super().__init__(spec, runtime)
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
         self.mixer = build_part("mixer", spec.mixer, runtime)
-        self.ffn_norm = build_part("norm", spec.ffn_norm, runtime)
-        self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime)
+        has_ffn = spec.feed_forward is not None
+        self.ffn_norm = build_part("norm", spec.ffn_norm, runtime) if has_ffn else None
+        self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime) if has_ffn else None
+        self.after = tuple(build_part("stream_input", s, runtime) for s in getattr(spec, "after", ()))
+        self.mult = float(getattr(spec, "residual_mult", 1.0))
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        own = (self.mixer_norm, self.mixer) + ((self.ffn_norm, self.feed_forward) if self.feed_forward is not None else ())
+        return own + self.after
 
     def declare(self):
         d = {}
@@ -37,11 +43,14 @@ class PreNormLayer(Layer):
     def forward(self, stream, ctx, cache):
         # A part that can, gets the norm folded into its first product and leaves its last product to the stream,
         # which folds it into the next norm (decode steps in bfloat16; everything else runs part by part).
-        mixer, ffn = self.mixer, self.feed_forward
+        mixer, ffn, mult = self.mixer, self.feed_forward, self.mult
         h = stream.normed(self.mixer_norm, fold_ok=mixer.accepts_folded)
-        stream.add(mixer.forward(h, ctx, cache, lazy_output=True) if mixer.lazy_output else mixer.forward(h, ctx, cache))
-        h = stream.normed(self.ffn_norm, fold_ok=ffn.accepts_folded)
-        stream.add(ffn.forward(h, ctx, lazy_output=True) if ffn.lazy_output else ffn.forward(h, ctx))
+        stream.add(mixer.forward(h, ctx, cache, lazy_output=True) if mixer.lazy_output else mixer.forward(h, ctx, cache), mult)
+        if ffn is not None:
+            h = stream.normed(self.ffn_norm, fold_ok=ffn.accepts_folded)
+            stream.add(ffn.forward(h, ctx, lazy_output=True) if ffn.lazy_output else ffn.forward(h, ctx), mult)
+        for part in self.after:
+            part.forward(stream, ctx, mult)
 
 
 register_part("layer", "pre_norm", PreNormLayer)

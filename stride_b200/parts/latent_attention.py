@@ -1,0 +1,142 @@
+"""Attention over a compressed cache (latent attention).
+
+Per token the layer keeps one latent vector ``c`` [kv_rank] (an RMS-normed projection of its input) and one rotated
+key part ``k_r`` [rot_dim] that all heads share. Head a has the query ``[q_a | q_rot_a]`` ([dim | rot_dim], the
+second part rotated by position), the key ``[W_uk_a c | k_r]`` and the value ``W_uv_a c``; scores are causal,
+softmaxed, and the head's output may be gated by ``sigmoid(W_g h)_a`` before the output projection.
+
+The keys and values are never formed. With ``q~_a = W_uk_a^T q_a`` the score is ``(q~_a . c + q_rot_a . k_r) * scale``
+and the output ``W_uv_a (sum_j p_j c_j)``: attention runs on the cached vectors themselves, with one key/value
+"head" of width kv_rank + rot_dim for all query heads, in prompts and in decoding alike. Steps:
+
+    one product     [W_q ; W_dkv ; W_g] h                          (``ops.linear``)
+    latent_prepare  norm of the latent, rotations, cache write     (one kernel)
+    head_gemm       q~ = W_uk^T q per head                         (one kernel)
+    attention       over the latent pages                          (one kernel)
+    head_gemm       W_uv per head, times the gate                  (one kernel)
+    output product  W_o                                            (left to the residual stream)
+
+A layer with ``own_latent`` False has no W_dkv: its run is scheduled on another layer's cache slot without writing
+it, and reads what that layer stored (latent after the norm, key part after the rotation).
+
+Spec: ``num_heads``, ``head_dim`` (the unrotated query/key width), ``scale``, ``position`` (a rotary table; its
+``head_dim`` is the number of rotated entries, pairs (2i, 2i+1)), params ``rot_dim``, ``value_dim``, ``kv_rank``,
+``latent_eps``, ``own_latent``, ``output_gate``. Tensors under the prefix: ``q``, ``dkv``, ``dkv.norm``, ``uk``, ``uv``,
+``g``, ``o``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import CacheRequest, Mixer, Projection, TensorDecl, build_part, register_part
+
+
+class LatentAttention(Mixer):
+    lazy_output = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        s, p = spec, dict(spec.params)
+        self.hidden, self.heads, self.dim = int(s.hidden), int(s.num_heads), int(s.head_dim)
+        self.rot, self.vdim, self.rank = int(p["rot_dim"]), int(p["value_dim"]), int(p["kv_rank"])
+        self.eps = float(p.get("latent_eps", 0.0))
+        self.own_latent = bool(p.get("own_latent", True))
+        self.gated = bool(p.get("output_gate", False))
+        self.scale = float(s.scale)
+        if min(self.heads, self.dim, self.vdim, self.rank) <= 0 or self.rot <= 0:
+            raise ValueError("latent attention needs positive heads, dim, rot_dim, value_dim and kv_rank")
+        if self.rank > 512:
+            raise ValueError(f"kv_rank {self.rank} is not supported by the latent attention kernel (up to 512 is)")
+        self.position = build_part("position", s.position, runtime)
+        self.rot_dims = int(s.position.head_dim)
+        if self.rot_dims > self.rot or self.rot_dims % 2:
+            raise ValueError(f"{self.rot_dims} rotated entries do not fit a rotated part of {self.rot}")
+        self.q_dim = self.heads * (self.dim + self.rot)
+        self.kv_dim = self.rank + self.rot if self.own_latent else 0
+        self.g_dim = self.heads if self.gated else 0
+        # columns of the fused product, each block starting at a multiple of 8 so that rows of 16-bit numbers stay
+        # 16-byte aligned inside it
+        self.q_off = 0
+        self.kv_off = -(-self.q_dim // 8) * 8
+        self.g_off = self.kv_off + -(-self.kv_dim // 8) * 8
+        self.proj_dim = -(-(self.g_off + self.g_dim) // 8) * 8
+        self.w_in = self.w_uk = self.w_uv = self.w_o = self.latent_w = None
+
+    # ----------------------------------------------------------------- weights
+    def _n(self, short):
+        return self.spec.prefix + short
+
+    def declare(self):
+        d = {self._n("q"): TensorDecl((self.q_dim, self.hidden)), self._n("uk"): TensorDecl((self.heads * self.dim, self.rank)),
+             self._n("uv"): TensorDecl((self.heads * self.vdim, self.rank)), self._n("o"): TensorDecl((self.hidden, self.heads * self.vdim))}
+        if self.own_latent:
+            d[self._n("dkv")] = TensorDecl((self.rank + self.rot, self.hidden))
+            d[self._n("dkv.norm")] = TensorDecl((self.rank,), "vector")
+        if self.gated:
+            d[self._n("g")] = TensorDecl((self.heads, self.hidden))
+        d.update(self.position.declare())
+        return d
+
+    def bind(self, weights):
+        q = weights[self._n("q")]
+        w = torch.zeros((self.proj_dim, self.hidden), dtype=q.dtype, device=q.device)
+        w[:self.q_dim] = q
+        if self.own_latent:
+            w[self.kv_off:self.kv_off + self.kv_dim] = weights[self._n("dkv")]
+            self.latent_w = weights[self._n("dkv.norm")]
+        if self.gated:
+            w[self.g_off:self.g_off + self.g_dim] = weights[self._n("g")]
+        self.w_in = w
+        self.w_uk, self.w_uv, self.w_o = weights[self._n("uk")], weights[self._n("uv")], weights[self._n("o")]
+        self.position.bind(weights)
+
+    def named_tensors(self):
+        out = {self._n("q"): self.w_in[:self.q_dim], self._n("uk"): self.w_uk, self._n("uv"): self.w_uv, self._n("o"): self.w_o}
+        if self.own_latent:
+            out[self._n("dkv")] = self.w_in[self.kv_off:self.kv_off + self.kv_dim]
+            out[self._n("dkv.norm")] = self.latent_w
+        if self.gated:
+            out[self._n("g")] = self.w_in[self.g_off:self.g_off + self.g_dim]
+        out.update(self.position.named_tensors())
+        return out
+
+    # ------------------------------------------------------------------- cache
+    def cache_request(self):
+        return CacheRequest(tensors=(("latent", 1, self.rank), ("key_rot", 1, self.rot)))
+
+    # ----------------------------------------------------------------- forward
+    def forward(self, x, ctx, cache, lazy_output: bool = False):
+        tokens = x.shape[0]
+        if self.own_latent != bool(cache.writes):
+            raise ValueError("a latent attention layer writes the cache exactly when it has a latent projection of its own")
+        proj = self.rt.buffer("latent_proj", tokens, self.proj_dim)
+        ops.linear(x, self.w_in, proj)
+        width = self.rank + self.rot
+        qa = self.rt.buffer("latent_q", tokens, self.heads * width)
+        latent, key_rot = cache.tensors["latent"], cache.tensors["key_rot"]
+        cos, sin = self.position.tables()
+        seq, pos = ctx.seq_of_token[:tokens], ctx.positions[:tokens]
+        ops.latent_prepare(proj, self.q_off, self.kv_off if self.own_latent else -1, qa, pos, seq,
+                           ctx.slot_mapping[cache.group][:tokens] if cache.writes else None, cos, sin, self.latent_w, self.eps,
+                           latent, key_rot, self.heads, self.dim, self.rot, self.rot_dims, self.rank)
+        # q~[t, a, :] = q[t, a, :dim] @ W_uk[a]          W_uk [heads * dim, rank]: B_a[k, n] = W_uk[a * dim + k, n]
+        ops.head_gemm(proj, self.proj_dim, self.dim + self.rot, self.w_uk, self.dim * self.rank, self.rank, 1, qa, self.heads * width, width,
+                      tokens, self.heads, self.rank, self.dim, a_off=self.q_off)
+        mixed = self.rt.buffer("latent_mixed", tokens, self.heads * self.rank)
+        ops.latent_attention(qa, mixed, latent, key_rot, ctx.block_table[cache.group], seq, pos, self.heads, self.rank, self.rot,
+                             cache.page_size, self.scale)
+        # o[t, a, :] = W_uv[a] mixed[t, a, :]            W_uv [heads * vdim, rank]: B_a[k, n] = W_uv[a * vdim + n, k]
+        attn = self.rt.buffer("latent_out", tokens, self.heads * self.vdim)
+        gate = proj if self.gated else None
+        ops.head_gemm(mixed, self.heads * self.rank, self.rank, self.w_uv, self.vdim * self.rank, 1, self.rank, attn, self.heads * self.vdim,
+                      self.vdim, tokens, self.heads, self.vdim, self.rank, gate=gate, ldg=self.proj_dim, gate_off=self.g_off)
+        if lazy_output:
+            return Projection(attn, self.w_o)
+        out = self.rt.buffer("mixer_out", tokens, self.hidden)
+        ops.linear(attn, self.w_o, out)
+        return out
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -45,6 +45,12 @@ class RotaryEncoding(PositionEncoding):
         self._tables = None
 
     def _build(self):
+        if dict(self.spec.params).get("angles") == "float64":
+            # angle = position * theta^(-2i/dims) formed in float64 and rounded once, to float32 tables: at position
+            # p a float32 product would be off by up to p * 2^-24 radians
+            exponent = torch.arange(0, self.spec.head_dim, 2, dtype=torch.float64) / max(self.spec.head_dim, 1)
+            angles = torch.outer(torch.arange(self.max_positions, dtype=torch.float64), float(self.spec.theta) ** -exponent)
+            return angles.cos().float().to(self.rt.device), angles.sin().float().to(self.rt.device)
         inv_freq = rope_inverse_frequencies(self.spec.head_dim, self.spec.theta, self.spec.scaling)
         angles = torch.outer(torch.arange(self.max_positions, dtype=torch.float32), inv_freq)
         return angles.cos().to(self.rt.device), angles.sin().to(self.rt.device)

@@ -76,20 +76,26 @@ class ResidualStream:
         self.hidden = hidden
         self.residual = runtime.buffer("residual", tokens, hidden, torch.float32)
         self._pending = None
+        self._scale = 1.0
 
-    def add(self, delta) -> None:
-        """``delta``: a tensor, or a ``Projection`` (a product not yet run) that the next ``normed`` may fold."""
+    def add(self, delta, scale: float = 1.0) -> None:
+        """``delta``: a tensor, or a ``Projection`` (a product not yet run) that the next ``normed`` may fold. The
+        stream grows by ``scale * delta`` (the multiplier some architectures put on every sum into the stream)."""
         self._settle()
         self._pending = delta
+        self._scale = float(scale)
 
     def _settle(self) -> None:
         """Applies what is pending to the residual."""
         if self._pending is not None:
             p = self._pending
-            if not (isinstance(p, Projection) and p.weight.shape[0] == self.hidden and ops.rows_wanted(self.tokens)
-                    and ops.linear_rows_add(p.x, p.weight, self.residual)):
+            if self._scale != 1.0:
+                ops.add_scaled(self.residual, self._run(p), self._scale)
+            elif not (isinstance(p, Projection) and p.weight.shape[0] == self.hidden and ops.rows_wanted(self.tokens)
+                      and ops.linear_rows_add(p.x, p.weight, self.residual)):
                 ops.add_residual(self.residual, self._run(p))
             self._pending = None
+            self._scale = 1.0
 
     def _run(self, pending):
         """The pending delta as a tensor (runs a deferred product)."""
@@ -105,6 +111,8 @@ class ResidualStream:
         takes an ``ops.FoldedNorm`` too: when the pending delta is a deferred product
         and the norm allows it, product, sum and the norm's statistics become one
         kernel and the norm's scaling is left to the consumer."""
+        if self._scale != 1.0:
+            return self._normed_scaled(norm, rows, tag)
         if rows is None and fold_ok and isinstance(self._pending, Projection):
             folded = self._fold(norm, tag)
             if folded is not None:
@@ -121,6 +129,23 @@ class ResidualStream:
             self._pending = pending
             out = self.rt.buffer(tag + "_rows", rows.shape[0], self.hidden, row_kind="rows")
             norm.apply(self.residual, pending, out, rows=rows)
+        return out
+
+    def _normed_scaled(self, norm, rows, tag):
+        """The same with a multiplier on the pending delta: a norm that takes it gets sum, write-back and norm in
+        its one kernel; for any other the sum is applied first."""
+        if not getattr(norm, "takes_scale", False):
+            self._settle()
+            return self.normed(norm, rows=rows, tag=tag)
+        pending, scale = self._run(self._pending), self._scale
+        if rows is None:
+            out = self.rt.buffer(tag, self.tokens, self.hidden)
+            norm.apply(self.residual, pending, out, scale=scale)
+            self._pending, self._scale = None, 1.0
+        else:
+            self._pending = pending
+            out = self.rt.buffer(tag + "_rows", rows.shape[0], self.hidden, row_kind="rows")
+            norm.apply(self.residual, pending, out, rows=rows, scale=scale)
         return out
 
     def _fold(self, norm, tag):
