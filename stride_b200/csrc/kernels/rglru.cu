@@ -10,7 +10,10 @@
 // 0 .. taps-2 are the last taps-1 inputs x (oldest first; zero before the sequence starts, which is what a fresh slot
 // holds), row taps-1 is S. Three kernels, run in this order on any mix of portions and single tokens:
 //   rglru_conv    u for every token (reads the tail of the state, writes nothing to it)
-//   rglru_gates   the block-diagonal products with a and the gated input in the epilogue
+//   rglru_gates   the block-diagonal products, with a - 1 and the gated input in the epilogue. a - 1 = expm1(log a) is
+//                 what is handed on: for a channel that forgets slowly a is 1 - 1e-4 or closer, where float32 has
+//                 steps of 6e-8, and the error of a rounded (and, with a biased exponential, shifted) a grows with
+//                 every token of a long sequence
 //   rglru_scan    the recurrence over each request's tokens, the output, and the new state (S and the tail)
 #include "common.cuh"
 
@@ -97,14 +100,14 @@ rglru_gates_kernel(const float* __restrict__ u, const T* __restrict__ wa_t, cons
         const float r = sigmoid_f(accr[tt] + br), g = sigmoid_f(acci[tt] + bg);
         const float log_a = -rate * r;
         const size_t at = static_cast<size_t>(t0 + tt) * width + c;
-        a_out[at] = expf(log_a);
+        a_out[at] = expm1f(log_a);      // a - 1: a itself, rounded to float32, would lose the rate of a slowly decaying channel
         gx_out[at] = sqrtf(-expm1f(2.f * log_a)) * g * us[tt * bw + oc];
     }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ gx, const T* __restrict__ xy, int ld, int x_off, int y_off,
+rglru_scan_kernel(const float* __restrict__ a /* a - 1 */, const float* __restrict__ gx, const T* __restrict__ xy, int ld, int x_off, int y_off,
                   const float* __restrict__ bias_x, const float* __restrict__ bias_y, float* __restrict__ state,
                   const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len, const int32_t* __restrict__ state_slot,
                   T* __restrict__ out, int width, int taps) {
@@ -120,7 +123,7 @@ rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ gx, con
     const float by = bias_y[c];
     for (int i = 0; i < n; ++i) {
         const size_t at = static_cast<size_t>(start + i) * width + c;
-        s = fmaf(a[at], s, gx[at]);
+        s = fmaf(a[at], s, s) + gx[at];         // a S + gx with a - 1 stored
         const float y = gelu_tanh_f(to_f32(xy[static_cast<size_t>(start + i) * ld + y_off + c]) + by);
         out[at] = from_f32<T>(s * y);
     }
