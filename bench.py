@@ -402,6 +402,117 @@ def run_profile(args) -> dict:
             "context": context, "steps": args.warmup + args.steps}
 
 
+# ------------------------------------------------------- two designs side by side
+# Layer sizes for `--compare nidilix`: the recurrent / latent-attention / routed design beside the dense Llama decoder of
+# the same width, depth, vocabulary and active feed-forward parameters per token. Random weights; a few layers only.
+COMPARE_SIZES = {
+    "w1024": dict(width=1024, vocab=32000, recurrent=dict(width=1280, blocks=8, conv=4),
+                  attention=dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256), experts=16, top=2, ff=512, shared=1024, side=64,
+                  llama_heads=8, llama_kv=2),
+    "w2048": dict(width=2048, vocab=32000, recurrent=dict(width=2560, blocks=10, conv=4),
+                  attention=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512), experts=32, top=4, ff=768, shared=1024, side=128,
+                  llama_heads=16, llama_kv=4),
+}
+
+
+def compare_configs(size: dict, layers: int):
+    """(Nidilix config.json, Llama config.json) of one size: layers cycle recurrent, recurrent, attention, the later
+    attention layers reading the first one's cache."""
+    import math
+    a = size["attention"]
+    mixer = dict(a, rot={"base": 10000.0, "dims": a["rot_dim"]}, scale=1.0 / math.sqrt(a["dim"] + a["rot_dim"]))
+    mlp = {"kind": "moe", "router": {"experts": size["experts"], "top": size["top"]}, "expert": {"ff": size["ff"]},
+           "shared": {"ff": size["shared"]}}
+    entries, first = [], None
+    for i in range(layers):
+        if i % 3 == 2:
+            m = dict(mixer)
+            if first is None:
+                first = i
+            else:
+                m["kv_from"] = first
+            entries.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+        else:
+            entries.append({"type": "rglru", "mixer": dict(size["recurrent"]), "mlp": mlp})
+    ours = {"architecture": "Nidilix", "width": size["width"], "vocab": size["vocab"], "residual_mult": 0.5, "norm": {"eps": 1e-6},
+            "token_side": {"dim": size["side"]}, "layers": entries}
+    inter = (size["top"] * size["ff"] + size["shared"]) * 2 // 3 // 64 * 64
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "hidden_size": size["width"],
+             "num_attention_heads": size["llama_heads"], "num_key_value_heads": size["llama_kv"], "head_dim": 128,
+             "intermediate_size": inter, "vocab_size": size["vocab"], "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": False, "max_position_embeddings": 8192, "hidden_act": "silu"}
+    return ours, llama
+
+
+def _measure_design(config: dict, batch: int, context: int, prompt_len: int, steps: int, warmup: int) -> dict:
+    """Prefill of one prompt and a decode step of ``batch`` requests at ``context`` for one configuration: device time
+    by CUDA events, and the device time per class of kernel of one eagerly run step of each."""
+    import torch
+
+    from stride_b200 import Engine
+
+    page = 16
+    need = batch * (context + page) + prompt_len + 4096
+    engine = Engine(config=config, random_weights=0, dtype="bfloat16", block_size=page, num_blocks=need // page + 64,
+                    max_batch_tokens=prompt_len, max_batch_seqs=max(batch, 8), max_model_len=context + 1024, prefix_caching=False,
+                    check_invariants=False)
+    for pages in engine.device_cache.pages:
+        pages.normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, engine.model.vocab, (prompt_len,), generator=g).tolist()
+
+    def prefill_step(key, timed=False):
+        engine.cache.open(key, "bench")
+        engine.cache.ensure(key, prompt_len, 0)
+        sb = engine._rt.StepBatch(engine.cache)
+        sb.add(key, prompt, 0, [prompt_len - 1])
+        if timed:
+            _, classes = engine.runner.timed_step(sb)
+            engine.cache.close(key)
+            return classes
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.runner.step(sb)
+        end.record()
+        torch.cuda.synchronize()
+        engine.cache.close(key)
+        return start.elapsed_time(end)
+
+    times = [prefill_step(900000 + i) for i in range(3 + 5)][3:]
+    prefill_ms = statistics.median(times)
+    prefill_classes = prefill_step(910000, timed=True)
+    step_batch, keys = _synthetic_decode_batch(engine, batch, context, 1000)
+    decode_ms, clocks, _ = _time_graph(engine, step_batch, steps, warmup)
+    _, decode_classes = engine.runner.timed_step(step_batch)
+    for key in keys:
+        engine.cache.close(key)
+    out = {"weights_mb": round(engine.model.weight_bytes() / 1e6, 1),
+           "prefill": {"tokens": prompt_len, "ms": round(prefill_ms, 3), "tokens_per_s": round(prompt_len / prefill_ms * 1e3, 1),
+                       "classes_us": _rounded(prefill_classes, 12)},
+           "decode": {"batch": batch, "context": context, "ms": round(decode_ms, 4), "tokens_per_s": round(batch / decode_ms * 1e3, 1),
+                      "classes_us": _rounded(decode_classes, 12)},
+           "clocks": clocks}
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_compare(args) -> dict:
+    """``--compare nidilix``: prefill and decode throughput of the Nidilix design at a few layer sizes beside the Llama
+    decoder at equal size, with the device time per class of kernel. Not the headline workload."""
+    layers = args.layers or 6
+    sizes = [s for s in args.compare_sizes.split(",") if s]
+    result = {"mode": "compare", "design": "nidilix", "beside": "llama", "layers": layers, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    for name in sizes:
+        ours, llama = compare_configs(COMPARE_SIZES[name], layers)
+        result["sizes"][name] = {
+            "nidilix": _measure_design(ours, args.batch, args.context, 2048, args.steps, args.warmup),
+            "llama": _measure_design(llama, args.batch, args.context, 2048, args.steps, args.warmup)}
+    return result
+
+
 # --------------------------------------------------------------------- reference
 def run_reference(args) -> dict:
     ref = os.path.join(ROOT, "baseline", "_ref")
@@ -498,6 +609,9 @@ def main(argv=None) -> int:
     p.add_argument("--no-breakdown", action="store_true", help="skip the per-class times of one decode step and the prefill")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="run a few eager steps of one kind for a profiler instead of measuring")
+    p.add_argument("--compare", choices=["nidilix"], default=None,
+                   help="instead of the headline workload: this design's prefill and decode beside the Llama decoder at equal size")
+    p.add_argument("--compare-sizes", default="w1024,w2048", help="comma-separated names of the sizes to compare")
     args = p.parse_args(argv)
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:
@@ -505,6 +619,11 @@ def main(argv=None) -> int:
         return 2
     if args.profile:
         print(json.dumps(run_profile(args)))
+        return 0
+    if args.compare:
+        if args.context == 8192:
+            args.context = 2048         # the comparison's own default
+        print(json.dumps(run_compare(args)))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

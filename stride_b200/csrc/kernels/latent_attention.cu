@@ -14,6 +14,7 @@
 //                     position 0 with an online softmax, so a token's result does not depend on how the step was
 //                     cut; float32 arithmetic in both storage types.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 namespace stride {
 
@@ -129,6 +130,39 @@ head_gemm_kernel(const T* __restrict__ A, int lda, int a_hs, const T* __restrict
             if (n < N) C[static_cast<size_t>(m) * ldc + static_cast<size_t>(a) * c_hs + n] = from_f32<T>(acc[i][j] * g);
         }
     }
+}
+
+// The same on the tensor cores for bfloat16 (mma_tile.cuh): 64 tokens x 64 columns of one head a CTA.
+__global__ void __launch_bounds__(128)
+head_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, int a_hs, const __nv_bfloat16* __restrict__ B, long long b_hs, int b_ks,
+                    int b_ns, __nv_bfloat16* __restrict__ C, int ldc, int c_hs, const __nv_bfloat16* __restrict__ gate, int ldg, int M,
+                    int N, int K) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ TileSmem sm;
+    const int a = blockIdx.y;
+    const int m0 = blockIdx.z * TM, n0 = blockIdx.x * TN;
+    for (int r = threadIdx.x; r < TM; r += 128)
+        sm.a_rows[r] = m0 + r < M ? A + static_cast<size_t>(m0 + r) * lda + static_cast<size_t>(a) * a_hs : nullptr;
+    __syncthreads();
+    float acc[2][4][4];
+    mma_tile_64x64(sm, B + static_cast<size_t>(a) * b_hs, b_ns, b_ks, n0, N, K, acc);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int x = 0; x < 4; x += 2) {
+            const int m = m0 + tile_row(i, x);
+            if (m >= M) continue;
+            float g = 1.f;
+            if (gate) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + a])));
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {
+                    const int n = n0 + tile_col(j, x + y);
+                    if (n < N) C[static_cast<size_t>(m) * ldc + static_cast<size_t>(a) * c_hs + n] = __float2bfloat16_rn(acc[i][j][x + y] * g);
+                }
+        }
 }
 
 // ------------------------------------------------------------------------------------------- exact attention
@@ -275,10 +309,12 @@ int stride_head_gemm(const void* A, int lda, int a_hs, const void* B, long long 
         stride::launch(head_gemm_kernel<float>, grid, dim3(256), 0, stream, static_cast<const float*>(A), lda, a_hs,
                        static_cast<const float*>(B), b_hs, b_ks, b_ns, static_cast<float*>(C), ldc, c_hs, static_cast<const float*>(gate),
                        ldg, M, N, K);
-    else if (dtype == STRIDE_DTYPE_BF16)
-        stride::launch(head_gemm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, a_hs,
+    else if (dtype == STRIDE_DTYPE_BF16) {
+        const dim3 tc_grid((N + TN - 1) / TN, heads, (M + TM - 1) / TM);
+        stride::launch(head_gemm_tc_kernel, tc_grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, a_hs,
                        static_cast<const __nv_bfloat16*>(B), b_hs, b_ks, b_ns, static_cast<__nv_bfloat16*>(C), ldc, c_hs,
                        static_cast<const __nv_bfloat16*>(gate), ldg, M, N, K);
+    }
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

@@ -1,0 +1,117 @@
+// A 64 x 64 output tile of C = A B^T in bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulators), for
+// the small products that sit between the library products of a layer: the per-head products of latent attention
+// and the experts' products, whose rows are scattered or ragged. Four warps, each 32 x 32 of the tile; operands are
+// staged in shared memory 32 columns of K at a time (rows padded to 40 elements: the fragment loads of a warp then fall
+// into 32 different banks) and read as the instruction's fragments with plain 32-bit loads.
+//
+//   A: row r of the tile starts at a_rows[r] (nullptr: the row is beyond the end and counts as zeros), K contiguous.
+//   B: element (n, k) at B[n * b_ns + k * b_ks]; either stride may be 1.
+// Every output element is a sum over k in the order of the instruction, the same for any tile and any batch, so a row's
+// result does not depend on what else is computed beside it.
+#pragma once
+
+#include "common.cuh"
+
+namespace stride {
+
+constexpr int TM = 64, TN = 64, TK = 32, TPAD = 40;
+
+struct __align__(16) TileSmem {
+    __nv_bfloat16 a[TM][TPAD];
+    __nv_bfloat16 b[TN][TPAD];
+    const __nv_bfloat16* a_rows[TM];
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// acc[i][j][.]: the warp's m16 tile i (rows wm * 32 + i * 16 ..) and n8 tile j (columns wn * 32 + j * 8 ..), wm = warp / 2,
+// wn = warp % 2. Element e of a fragment: row (lane / 4) + 8 * (e / 2), column 2 * (lane % 4) + (e % 2).
+// Call with 128 threads; sm.a_rows must be filled and visible (__syncthreads) before.
+__device__ __forceinline__ void mma_tile_64x64(TileSmem& sm, const __nv_bfloat16* __restrict__ B, long long b_ns, long long b_ks, int n0,
+                                               int N, int K, float (&acc)[2][4][4]) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += TK) {
+        // A: 64 rows x 4 chunks of 8 elements
+        for (int c = tid; c < TM * 4; c += 128) {
+            const int r = c >> 2, kc = (c & 3) * 8;
+            const __nv_bfloat16* src = sm.a_rows[r];
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (src) {
+                src += k0 + kc;
+                if (k0 + kc + 8 <= K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                    v = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+                    for (int x = 0; x < 8; ++x)
+                        if (k0 + kc + x < K) e[x] = src[x];
+                }
+            }
+            *reinterpret_cast<uint4*>(&sm.a[r][kc]) = v;
+        }
+        if (b_ks == 1) {
+            for (int c = tid; c < TN * 4; c += 128) {
+                const int n = c >> 2, kc = (c & 3) * 8;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (n0 + n < N) {
+                    const __nv_bfloat16* src = B + static_cast<long long>(n0 + n) * b_ns + k0 + kc;
+                    if (k0 + kc + 8 <= K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                        v = *reinterpret_cast<const uint4*>(src);
+                    } else {
+                        __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+                        for (int x = 0; x < 8; ++x)
+                            if (k0 + kc + x < K) e[x] = src[x];
+                    }
+                }
+                *reinterpret_cast<uint4*>(&sm.b[n][kc]) = v;
+            }
+        } else {        // n contiguous in memory: neighbouring threads read neighbouring n
+            for (int c = tid; c < TN * TK; c += 128) {
+                const int k = c / TN, n = c % TN;
+                sm.b[n][k] = (n0 + n < N && k0 + k < K) ? B[static_cast<long long>(n0 + n) * b_ns + static_cast<long long>(k0 + k) * b_ks]
+                                                        : __float2bfloat16_rn(0.f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; kk += 16) {
+            uint32_t af[2][4], bf[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm * 32 + i * 16 + g;
+                af[i][0] = *reinterpret_cast<const uint32_t*>(&sm.a[r][kk + 2 * t]);
+                af[i][1] = *reinterpret_cast<const uint32_t*>(&sm.a[r + 8][kk + 2 * t]);
+                af[i][2] = *reinterpret_cast<const uint32_t*>(&sm.a[r][kk + 2 * t + 8]);
+                af[i][3] = *reinterpret_cast<const uint32_t*>(&sm.a[r + 8][kk + 2 * t + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = wn * 32 + j * 8 + g;
+                bf[j][0] = *reinterpret_cast<const uint32_t*>(&sm.b[n][kk + 2 * t]);
+                bf[j][1] = *reinterpret_cast<const uint32_t*>(&sm.b[n][kk + 2 * t + 8]);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], af[i], bf[j]);
+        }
+        __syncthreads();
+    }
+}
+
+// Row and column (inside the tile) of element e of acc[i][j].
+__device__ __forceinline__ int tile_row(int i, int e) { return ((threadIdx.x >> 5) >> 1) * 32 + i * 16 + ((threadIdx.x & 31) >> 2) + 8 * (e >> 1); }
+__device__ __forceinline__ int tile_col(int j, int e) { return ((threadIdx.x >> 5) & 1) * 32 + j * 8 + 2 * (threadIdx.x & 3) + (e & 1); }
+
+}  // namespace stride

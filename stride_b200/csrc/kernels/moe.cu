@@ -10,6 +10,7 @@
 //   moe_combine   out[t] = sum_k weight[t, k] * Y[row_of[t, k]] (+ a shared expert's output), in the order of k.
 // A row's result depends only on that row: not on the batch, nor on where the plan put it.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 namespace stride {
 
@@ -187,6 +188,52 @@ grouped_gemm_kernel(const TA* __restrict__ A, int lda, const int32_t* __restrict
     }
 }
 
+// The same on the tensor cores for bfloat16 operands (mma_tile.cuh): 128 threads a tile.
+template <typename TC>
+__global__ void __launch_bounds__(128)
+grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int32_t* __restrict__ row_map,
+                       const __nv_bfloat16* __restrict__ W, const int32_t* __restrict__ offsets, int experts, TC* __restrict__ C, int ldc,
+                       int N, int K, int act) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ TileSmem sm;
+    int tile = blockIdx.y, e = 0, m0 = 0, m_end = 0;
+    for (; e < experts; ++e) {
+        const int lo = offsets[e], hi = offsets[e + 1];
+        const int tiles = (hi - lo + TM - 1) / TM;
+        if (tile < tiles) {
+            m0 = lo + tile * TM;
+            m_end = hi;
+            break;
+        }
+        tile -= tiles;
+    }
+    if (e >= experts) return;
+    const int n0 = blockIdx.x * TN;
+    for (int r = threadIdx.x; r < TM; r += 128) {
+        const int m = m0 + r;
+        sm.a_rows[r] = m < m_end ? A + static_cast<size_t>(row_map ? row_map[m] : m) * lda : nullptr;
+    }
+    __syncthreads();
+    float acc[2][4][4];
+    mma_tile_64x64(sm, W + static_cast<size_t>(e) * N * K, K, 1, n0, N, K, acc);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int m = m0 + tile_row(i, x), n = n0 + tile_col(j, x);
+                if (m >= m_end || n >= N) continue;
+                float v = acc[i][j][x];
+                if (act == 1) {
+                    v = fmaxf(v, 0.f);
+                    v *= v;
+                }
+                C[static_cast<size_t>(m) * ldc + n] = from_f32<TC>(v);
+            }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ Y, const int32_t* __restrict__ row_of, const float* __restrict__ weights,
@@ -247,7 +294,8 @@ int stride_moe_plan(const int32_t* ids, int tokens, int top, int experts, int32_
     return STRIDE_LAUNCH_STATUS();
 }
 
-// kind: 0 = everything float32; 1 = bfloat16 A and W, bfloat16 C; 2 = bfloat16 A and W, float32 C.
+// kind: 0 = everything float32 (FMA); 1 = bfloat16 A and W, bfloat16 C; 2 = bfloat16 A and W, float32 C (both on the
+// tensor cores); 3 = as 2 on the FMA kernel.
 int stride_grouped_gemm(const void* A, int lda, const int32_t* row_map, const void* W, const int32_t* offsets, int experts, void* C,
                         int ldc, int max_rows, int N, int K, int act, int kind, cudaStream_t stream) {
     if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || ldc < N) return STRIDE_BAD_ARGUMENT;
@@ -255,17 +303,20 @@ int stride_grouped_gemm(const void* A, int lda, const int32_t* row_map, const vo
     const int max_tiles = (max_rows + GM - 1) / GM + experts;       // no expert has more than one ragged tile
     if (max_tiles > 65535) return STRIDE_UNSUPPORTED;
     const dim3 grid((N + GN - 1) / GN, max_tiles);
-    if (kind == 0)
-        stride::launch(grouped_gemm_kernel<float, float, float>, grid, dim3(256), 0, stream, static_cast<const float*>(A), lda, row_map,
-                       static_cast<const float*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act);
-    else if (kind == 1)
-        stride::launch(grouped_gemm_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream,
-                       static_cast<const __nv_bfloat16*>(A), lda, row_map, static_cast<const __nv_bfloat16*>(W), offsets, experts,
-                       static_cast<__nv_bfloat16*>(C), ldc, N, K, act);
+    static_assert(GM == TM && GN == TN, "both forms of the grouped product use tiles of one size");
+    if (kind == 1)
+        stride::launch(grouped_gemm_tc_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, row_map,
+                       static_cast<const __nv_bfloat16*>(W), offsets, experts, static_cast<__nv_bfloat16*>(C), ldc, N, K, act);
     else if (kind == 2)
+        stride::launch(grouped_gemm_tc_kernel<float>, grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, row_map,
+                       static_cast<const __nv_bfloat16*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act);
+    else if (kind == 3)     // bfloat16 operands on the FMA kernel (kept for comparison)
         stride::launch(grouped_gemm_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, dim3(256), 0, stream,
                        static_cast<const __nv_bfloat16*>(A), lda, row_map, static_cast<const __nv_bfloat16*>(W), offsets, experts,
                        static_cast<float*>(C), ldc, N, K, act);
+    else if (kind == 0)
+        stride::launch(grouped_gemm_kernel<float, float, float>, grid, dim3(256), 0, stream, static_cast<const float*>(A), lda, row_map,
+                       static_cast<const float*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();
