@@ -9,10 +9,12 @@
 //                     rotated part of every query head (pairs (2i, 2i+1), angle from a float32 table), writes the
 //                     latent and the key part into their pages and the rotated queries beside the folded ones;
 //   head_gemm         the per-head products with W_uk (folding) and W_uv (unfolding, with an optional sigmoid gate
-//                     per (token, head) in its epilogue): float32 FMA, fixed k order;
+//                     per (token, head) in its epilogue): float32 FMA with a fixed k order for float32 operands,
+//                     tensor-core tiles (mma_tile.cuh) for bfloat16;
 //   latent_attention  the exact kernel: one warp per (token, head), keys walked in groups of 32 aligned to
 //                     position 0 with an online softmax, so a token's result does not depend on how the step was
-//                     cut; float32 arithmetic in both storage types.
+//                     cut; float32 arithmetic in both storage types. (The bfloat16 kernel on the tensor cores is
+//                     latent_attention_tc.cu.)
 #include "common.cuh"
 #include "mma_tile.cuh"
 

@@ -1,12 +1,14 @@
 // Routed feed-forward: each token goes to the `top` experts with the largest router logits.
 //
 //   moe_route     router logits z = W_r h + b in float32 (one warp per token), the top entries (the lower index wins
-//                 among equals), and the softmax over the chosen logits only;
+//                 among equals), and the softmax over the chosen logits only; moe_select is the choice alone, from
+//                 logits that a matrix product with float32 output has made (what the part runs);
 //   moe_plan      one CTA counts the rows of every expert, lays the (token, choice) pairs out expert by expert and
 //                 writes where each pair went: `offsets` [experts + 1], `perm_token` [rows] and `row_of` [tokens, top];
 //   grouped_gemm  C[p, :] = act(A[src(p), :] W[e(p)]^T) for the rows p of every expert e, the tiles of all experts in
 //                 one launch (the CTA finds its expert from `offsets` on the device, so nothing goes back to the
-//                 host and the step can be replayed from a graph); float32 FMA with a fixed k order;
+//                 host and the step can be replayed from a graph); float32 FMA with a fixed k order for float32
+//                 operands, tensor-core tiles (mma_tile.cuh) for bfloat16;
 //   moe_combine   out[t] = sum_k weight[t, k] * Y[row_of[t, k]] (+ a shared expert's output), in the order of k.
 // A row's result depends only on that row: not on the batch, nor on where the plan put it.
 #include "common.cuh"
@@ -67,6 +69,59 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
 #pragma unroll
         for (int i = 0; i < kMaxExperts / 32; ++i)
             if (i * 32 + lane == best_e) z[i] = -INFINITY;       // taken
+        if (k == 0) first = best;
+        const float p = expf(best - first);
+        denom += p;
+        if (lane == k) { mine = p; mine_id = best_e; }
+    }
+    if (lane < top) {
+        ids[static_cast<size_t>(t) * top + lane] = mine_id;
+        weights[static_cast<size_t>(t) * top + lane] = mine / denom;
+    }
+}
+
+// The choice alone, from logits a matrix product has made: z = logits + bias in float32, the same top rule and softmax.
+__global__ void __launch_bounds__(128)
+moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, const int32_t* __restrict__ seq_of_token,
+                  int32_t* __restrict__ ids, float* __restrict__ weights, int tokens, int experts, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    if (seq_of_token && seq_of_token[t] < 0) {
+        for (int k = lane; k < top; k += 32) {
+            ids[static_cast<size_t>(t) * top + k] = -1;
+            weights[static_cast<size_t>(t) * top + k] = 0.f;
+        }
+        return;
+    }
+    float z[kMaxExperts / 32];
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+        const int e = i * 32 + lane;
+        z[i] = e < experts ? logits[static_cast<size_t>(t) * experts + e] + (bias ? bias[e] : 0.f) : -INFINITY;
+    }
+    float first = 0.f, denom = 0.f, mine = 0.f;
+    int mine_id = -1;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = i * 32 + lane;
+            if (e < experts && (z[i] > best)) { best = z[i]; best_e = e; }
+        }
+        if (best == -INFINITY) best_e = 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i)
+            if (i * 32 + lane == best_e) z[i] = -INFINITY;
         if (k == 0) first = best;
         const float p = expf(best - first);
         denom += p;
@@ -283,6 +338,15 @@ int stride_moe_route(const void* h, const void* w_router, const float* bias, con
                        static_cast<const __nv_bfloat16*>(w_router), bias, seq_of_token, ids, weights, tokens, hidden, experts, top);
     else
         return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_moe_select(const float* logits, const float* bias, const int32_t* seq_of_token, int32_t* ids, float* weights, int tokens,
+                      int experts, int top, cudaStream_t stream) {
+    if (tokens < 0 || experts <= 0 || top <= 0 || top > experts) return STRIDE_BAD_ARGUMENT;
+    if (experts > kMaxExperts || top > kMaxTop) return STRIDE_UNSUPPORTED;
+    if (tokens == 0) return 0;
+    stride::launch(moe_select_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, logits, bias, seq_of_token, ids, weights, tokens, experts, top);
     return STRIDE_LAUNCH_STATUS();
 }
 

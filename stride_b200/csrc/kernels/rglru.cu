@@ -106,7 +106,7 @@ rglru_gates_kernel(const float* __restrict__ u, const T* __restrict__ wa_t, cons
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(64)
 rglru_scan_kernel(const float* __restrict__ a /* a - 1 */, const float* __restrict__ gx, const T* __restrict__ xy, int ld, int x_off, int y_off,
                   const float* __restrict__ bias_x, const float* __restrict__ bias_y, float* __restrict__ state,
                   const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len, const int32_t* __restrict__ state_slot,
@@ -121,6 +121,8 @@ rglru_scan_kernel(const float* __restrict__ a /* a - 1 */, const float* __restri
     float* rows = state + static_cast<size_t>(state_slot[seq]) * taps * width;
     float s = rows[static_cast<size_t>(taps - 1) * width + c];
     const float by = bias_y[c];
+    // nothing the loop loads depends on s: unrolled, eight tokens' loads are in flight while the chain of s runs
+#pragma unroll 8
     for (int i = 0; i < n; ++i) {
         const size_t at = static_cast<size_t>(start + i) * width + c;
         s = fmaf(a[at], s, s) + gx[at];         // a S + gx with a - 1 stored
@@ -189,12 +191,12 @@ int stride_rglru_scan(const float* a, const float* gx, const void* xy, int ld, i
     if (num_seqs < 0 || width <= 0 || taps <= 0 || num_seqs > 65535) return STRIDE_BAD_ARGUMENT;
     if (taps > kMaxTaps) return STRIDE_UNSUPPORTED;
     if (num_seqs == 0) return 0;
-    const dim3 grid((width + 127) / 128, num_seqs);
+    const dim3 grid((width + 63) / 64, num_seqs);
     if (dtype == STRIDE_DTYPE_F32)
-        stride::launch(rglru_scan_kernel<float>, grid, dim3(128), 0, stream, a, gx, static_cast<const float*>(xy), ld, x_off, y_off, bias_x,
+        stride::launch(rglru_scan_kernel<float>, grid, dim3(64), 0, stream, a, gx, static_cast<const float*>(xy), ld, x_off, y_off, bias_x,
                        bias_y, state, q_start, q_len, state_slot, static_cast<float*>(out), width, taps);
     else if (dtype == STRIDE_DTYPE_BF16)
-        stride::launch(rglru_scan_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a, gx, static_cast<const __nv_bfloat16*>(xy), ld, x_off,
+        stride::launch(rglru_scan_kernel<__nv_bfloat16>, grid, dim3(64), 0, stream, a, gx, static_cast<const __nv_bfloat16*>(xy), ld, x_off,
                        y_off, bias_x, bias_y, state, q_start, q_len, state_slot, static_cast<__nv_bfloat16*>(out), width, taps);
     else
         return STRIDE_BAD_ARGUMENT;

@@ -9,6 +9,7 @@ compiler or a size that a kernel refuses raises an error.
 from __future__ import annotations
 
 import ctypes
+import os as _os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -88,6 +89,13 @@ _SIGNATURES = {
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_latent_attention": ("latent_attention", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                                      c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "stride_latent_attention_tc": ("latent_attention_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                           c_float, c_int, c_int, c_void_p]),
+    "stride_side_gate": ("token_side", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "stride_side_norm_add": ("token_side", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "stride_cast_rows": ("token_side", [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
+    "stride_moe_select": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "stride_rglru_conv": ("rglru", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_int, c_int, c_int, c_int, c_void_p]),
     "stride_rglru_gates": ("rglru", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
@@ -126,7 +134,9 @@ _CLASS_OF = {
     "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling", "stride_sample_ranked": "sampling",
     "stride_add_dyt": "norm", "stride_add_scaled": "residual sum", "stride_token_side": "token side input",
     "stride_latent_prepare": "latent norm + rotation + cache write", "stride_head_gemm": "per-head product",
-    "stride_latent_attention": "attention (latent, exact kernel)", "stride_rglru_conv": "recurrent block: convolution",
+    "stride_latent_attention": "attention (latent, exact kernel)", "stride_latent_attention_tc": "attention (latent, tensor cores)",
+    "stride_side_gate": "token side input", "stride_side_norm_add": "token side input", "stride_cast_rows": "token side input",
+    "stride_moe_select": "router", "stride_rglru_conv": "recurrent block: convolution",
     "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_moe_route": "router",
     "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
     "stride_relu_squared": "relu^2",
@@ -313,7 +323,8 @@ def add_scaled(residual, delta, scale: float) -> None:
 
 def token_side(residual, ids, seq_of_token, table, offset: int, w_gate, w_proj, norm_w, eps: float, scale: float) -> None:
     """``residual[t] += scale * unit_rms(w_proj (gelu_tanh(w_gate residual[t]) * table[ids[t], offset:offset+dim])) * norm_w``,
-    in float32 on the stream itself. ``w_gate`` [dim, hidden], ``w_proj`` [hidden, dim]."""
+    in float32 on the stream itself, one CTA a token (the matrices are read once per token: for checks and small sizes;
+    the part runs the two products as products). ``w_gate`` [dim, hidden], ``w_proj`` [hidden, dim]."""
     tokens, hidden = residual.shape
     dim = w_gate.shape[0]
     if w_gate.shape != (dim, hidden) or w_proj.shape != (hidden, dim) or table.dtype != w_gate.dtype or w_proj.dtype != w_gate.dtype:
@@ -322,6 +333,27 @@ def token_side(residual, ids, seq_of_token, table, offset: int, w_gate, w_proj, 
                                     _opt(seq_of_token, "seq_of_token", torch.int32), _dev(table, "table"), table.shape[1], int(offset),
                                     table.shape[0], _dev(w_gate, "w_gate"), _dev(w_proj, "w_proj"), _dev(norm_w, "norm_w", torch.float32),
                                     tokens, hidden, dim, float(eps), float(scale), _code(w_gate.dtype), _stream()), "token_side")
+
+
+def cast_rows(src, dst) -> None:
+    """``dst = src`` (float32) rounded to ``dst``'s element type."""
+    _check(_fn("stride_cast_rows")(_dev(src, "src", torch.float32), _dev(dst, "dst"), src.numel(), _code(dst.dtype), _stream()), "cast_rows")
+
+
+def side_gate(pre, ids, seq_of_token, table, offset: int, out) -> None:
+    """``out[t] = gelu_tanh(pre[t]) * table[ids[t], offset : offset + dim]`` (zeros for a padded row)."""
+    tokens, dim = out.shape
+    _check(_fn("stride_side_gate")(_dev(pre, "pre", out.dtype), _dev(ids, "ids", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
+                                   _dev(table, "table", out.dtype), table.shape[1], int(offset), table.shape[0], _dev(out, "out"), tokens, dim,
+                                   _code(out.dtype), _stream()), "side_gate")
+
+
+def side_norm_add(residual, y, seq_of_token, norm_w, eps: float, scale: float) -> None:
+    """``residual[t] += scale * y[t] / sqrt(mean(y[t]^2) + eps) * norm_w`` in float32; padded rows stay."""
+    tokens, hidden = residual.shape
+    _check(_fn("stride_side_norm_add")(_dev(residual, "residual", torch.float32), _dev(y, "y"), _opt(seq_of_token, "seq_of_token", torch.int32),
+                                       _dev(norm_w, "norm_w", torch.float32), tokens, hidden, float(eps), float(scale), _code(y.dtype),
+                                       _stream()), "side_norm_add")
 
 
 # --------------------------------------------------------------- latent attention
@@ -370,6 +402,30 @@ def latent_attention(qa, out, latent_pages, krot_pages, block_table, seq_of_toke
         "latent_attention")
 
 
+def latent_tc_supported(dtype, heads: int, rank: int, rot: int) -> bool:
+    """Sizes the tensor-core latent attention kernel takes; everything else runs the exact kernel."""
+    return LATENT_TC and dtype == torch.bfloat16 and rank % 16 == 0 and rot % 16 == 0 and 0 < rank <= 512 and rank + rot <= 640
+
+
+LATENT_TC = _os.environ.get("STRIDE_B200_LATENT_TC", "1") != "0"
+
+
+def latent_attention_tc(qa, out, partial, latent_pages, krot_pages, block_table, q_start, q_len, ctx_len, seq_of_token, first_seq: int,
+                        num_seqs: int, first_token: int, tokens: int, max_q_len: int, heads: int, rank: int, rot: int, page_size: int,
+                        scale: float, splits: int = 1, keys_per_split: int = 0) -> None:
+    """Latent attention on the tensor cores for the requests ``first_seq .. first_seq + num_seqs`` of the step, which own
+    ``tokens`` rows from ``first_token`` on (``qa`` and ``out`` are the whole step's). ``max_q_len`` 1 runs the single-token
+    form, whose keys may be cut into ``splits`` of ``keys_per_split`` with ``partial`` (float32,
+    (first_token + tokens) * heads * splits * (rank + 2)) as scratch."""
+    _check(_fn("stride_latent_attention_tc")(
+        _dev(qa, "qa", torch.bfloat16), _dev(out, "out", torch.bfloat16), _opt(partial, "partial", torch.float32),
+        _dev(latent_pages, "latent_pages", torch.bfloat16), _dev(krot_pages, "krot_pages", torch.bfloat16),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(q_start, "q_start", torch.int32),
+        _dev(q_len, "q_len", torch.int32), _dev(ctx_len, "ctx_len", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+        first_seq, num_seqs, first_token, tokens, max_q_len, heads, rank, rot, page_size, float(scale), splits, keys_per_split, _stream()),
+        "latent_attention_tc")
+
+
 # ---------------------------------------------------------------- recurrent block
 def rglru_conv(xy, x_off: int, bias_x, conv_w, conv_b, state, seq_of_token, q_start, state_slot, u) -> None:
     tokens, width = u.shape
@@ -406,6 +462,15 @@ def moe_route(h, w_router, bias, seq_of_token, ids, weights) -> None:
     _check(_fn("stride_moe_route")(_dev(h, "h"), _dev(w_router, "w_router", h.dtype), _opt(bias, "bias", torch.float32),
                                    _opt(seq_of_token, "seq_of_token", torch.int32), _dev(ids, "ids", torch.int32),
                                    _dev(weights, "weights", torch.float32), tokens, hidden, experts, top, _code(h.dtype), _stream()), "moe_route")
+
+
+def moe_select(logits, bias, seq_of_token, ids, weights) -> None:
+    """From router logits [tokens, experts] (float32, without the bias): the ``top`` largest of ``logits + bias`` (the lower
+    index among equals) and the softmax over them."""
+    tokens, experts = logits.shape
+    _check(_fn("stride_moe_select")(_dev(logits, "logits", torch.float32), _opt(bias, "bias", torch.float32),
+                                    _opt(seq_of_token, "seq_of_token", torch.int32), _dev(ids, "ids", torch.int32),
+                                    _dev(weights, "weights", torch.float32), tokens, experts, ids.shape[1], _stream()), "moe_select")
 
 
 def moe_plan(ids, experts: int, offsets, perm_token, row_of, rank_tmp) -> None:

@@ -12,7 +12,9 @@ and the output ``W_uv_a (sum_j p_j c_j)``: attention runs on the cached vectors 
     one product     [W_q ; W_dkv ; W_g] h                          (``ops.linear``)
     latent_prepare  norm of the latent, rotations, cache write     (one kernel)
     head_gemm       q~ = W_uk^T q per head                         (one kernel)
-    attention       over the latent pages                          (one kernel)
+    attention       over the latent pages                          (tensor cores in bfloat16 where rank and rot_dim
+                                                                    are multiples of 16; the exact kernel otherwise
+                                                                    and for the whole 32-bit path)
     head_gemm       W_uv per head, times the gate                  (one kernel)
     output product  W_o                                            (left to the residual stream)
 
@@ -63,6 +65,7 @@ class LatentAttention(Mixer):
         self.g_off = self.kv_off + -(-self.kv_dim // 8) * 8
         self.proj_dim = -(-(self.g_off + self.g_dim) // 8) * 8
         self.w_in = self.w_uk = self.w_uv = self.w_o = self.latent_w = None
+        self._fast = ops.latent_tc_supported(runtime.dtype, self.heads, self.rank, self.rot)
 
     # ----------------------------------------------------------------- weights
     def _n(self, short):
@@ -125,8 +128,7 @@ class LatentAttention(Mixer):
         ops.head_gemm(proj, self.proj_dim, self.dim + self.rot, self.w_uk, self.dim * self.rank, self.rank, 1, qa, self.heads * width, width,
                       tokens, self.heads, self.rank, self.dim, a_off=self.q_off)
         mixed = self.rt.buffer("latent_mixed", tokens, self.heads * self.rank)
-        ops.latent_attention(qa, mixed, latent, key_rot, ctx.block_table[cache.group], seq, pos, self.heads, self.rank, self.rot,
-                             cache.page_size, self.scale)
+        self._attend(qa, mixed, latent, key_rot, ctx, cache, tokens)
         # o[t, a, :] = W_uv[a] mixed[t, a, :]            W_uv [heads * vdim, rank]: B_a[k, n] = W_uv[a * vdim + n, k]
         attn = self.rt.buffer("latent_out", tokens, self.heads * self.vdim)
         gate = proj if self.gated else None
@@ -137,6 +139,32 @@ class LatentAttention(Mixer):
         out = self.rt.buffer("mixer_out", tokens, self.hidden)
         ops.linear(attn, self.w_o, out)
         return out
+
+
+    def _attend(self, qa, mixed, latent, key_rot, ctx, cache, tokens):
+        table = ctx.block_table[cache.group]
+        if not self._fast:
+            # the exact kernel: the whole 32-bit path, and sizes the tensor-core kernel refuses
+            ops.latent_attention(qa, mixed, latent, key_rot, table, ctx.seq_of_token[:tokens], ctx.positions[:tokens], self.heads, self.rank,
+                                 self.rot, cache.page_size, self.scale)
+            return
+        geometry = (self.heads, self.rank, self.rot, cache.page_size, self.scale)
+        split = min(ctx.decode_tail_start, tokens)          # portions before, single tokens after
+        if split > 0:
+            ops.latent_attention_tc(qa, mixed, None, latent, key_rot, table, ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.seq_of_token, 0,
+                                    ctx.decode_tail_seq, 0, split, max(ctx.max_q_len, 2), *geometry)
+        if tokens > split:
+            n = tokens - split
+            # enough CTAs to fill the device, no split shorter than 256 keys
+            tiles = n * -(-self.heads // 16)
+            splits = max(1, min(-(-ctx.context_bound // 256), -(-296 // tiles), 64))
+            per_split = -(-(-(-ctx.context_bound // splits)) // 64) * 64
+            splits = max(1, -(-ctx.context_bound // per_split))
+            partial = None
+            if splits > 1:
+                partial = self.rt.scratch("latent_splits", tokens * self.heads * splits * (self.rank + 2))
+            ops.latent_attention_tc(qa, mixed, partial, latent, key_rot, table, ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.seq_of_token,
+                                    ctx.decode_tail_seq, n, split, n, 1, *geometry, splits=splits, keys_per_split=per_split)
 
 
 register_part("mixer", "latent_attention", LatentAttention)

@@ -4,7 +4,7 @@ Router logits ``z = W_r h + b`` in float32; a token uses the ``top`` experts wit
 the softmax over those logits only; an expert is ``W_down act(W_up h)`` without biases, ``act`` the square of relu;
 a shared expert of the same form runs for every token and is added.
 
-On the device: the router kernel chooses, a one-CTA plan lays the (token, choice) pairs out expert by expert, two
+On the device: the router's product leaves float32 logits, a kernel chooses, a one-CTA plan lays the (token, choice) pairs out expert by expert, two
 grouped products run all experts' rows in one launch each (the first gathers its rows through the plan and applies
 the activation, the second leaves float32 rows), and one kernel sums a token's rows with its weights and the
 shared expert's output. Nothing returns to the host, so a step can be captured in a graph.
@@ -74,7 +74,9 @@ class RoutedExperts(FeedForward):
         i32 = torch.int32
         ids = self.rt.buffer("moe_ids", tokens, top, i32)
         weights = self.rt.buffer("moe_weights", tokens, top, torch.float32)
-        ops.moe_route(x, self.w_router, self.bias, ctx.seq_of_token[:tokens], ids, weights)
+        logits = self.rt.buffer("moe_logits", tokens, self.experts, torch.float32)
+        ops.linear(x, self.w_router, logits)            # float32 sums of exact products, float32 logits
+        ops.moe_select(logits, self.bias, ctx.seq_of_token[:tokens], ids, weights)
         row_of = self.rt.buffer("moe_row_of", tokens, top, i32)
         perm = self.rt.buffer("moe_perm", tokens, top, i32).view(-1)
         rank = self.rt.buffer("moe_rank", tokens, top, i32).view(-1)

@@ -7,9 +7,13 @@ the stream itself.
     x <- x + scale * y / sqrt(mean(y^2) + eps) * norm_weight
 
 Tensors: the table under ``spec.table_name`` (one copy on the device for all layers), ``<prefix>gate`` [dim, hidden],
-``<prefix>proj`` [hidden, dim], ``<prefix>norm`` [hidden]. One kernel on the float32 stream."""
+``<prefix>proj`` [hidden, dim], ``<prefix>norm`` [hidden]. The two products run as matrix products (on the stream rounded
+to the compute type; the 32-bit path reads the float32 stream itself), the rest in two small kernels; the normalisation
+and the sum into the stream are float32."""
 
 from __future__ import annotations
+
+import torch
 
 from ..csrc import ops
 from .base import StreamInput, TensorDecl, register_part
@@ -45,9 +49,20 @@ class TokenSideInput(StreamInput):
 
     def forward(self, stream, ctx, scale: float) -> None:
         x = stream.materialize()
-        tokens = x.shape[0]
-        ops.token_side(x, ctx.token_ids[:tokens], ctx.seq_of_token[:tokens], self.table, self.spec.offset, self.gate, self.proj,
-                       self.norm, self.spec.eps, scale)
+        tokens, s = x.shape[0], self.spec
+        ids, seq = ctx.token_ids[:tokens], ctx.seq_of_token[:tokens]
+        if self.rt.dtype == torch.float32:
+            rounded = x
+        else:
+            rounded = self.rt.buffer("side_x", tokens, s.hidden)
+            ops.cast_rows(x, rounded)
+        pre = self.rt.buffer("side_pre", tokens, s.dim)
+        ops.linear(rounded, self.gate, pre)
+        gated = self.rt.buffer("side_gated", tokens, s.dim)
+        ops.side_gate(pre, ids, seq, self.table, s.offset, gated)
+        y = self.rt.buffer("side_y", tokens, s.hidden)
+        ops.linear(gated, self.proj, y)
+        ops.side_norm_add(x, y, seq, self.norm, s.eps, scale)
 
 
 register_part("stream_input", "token_side", TokenSideInput)

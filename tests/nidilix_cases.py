@@ -57,7 +57,16 @@ CASE_C = config(64, 97, [
     (recurrent(96, 2, 2), moe(2, 1, 24, shared=8)),
 ], mult=0.25, eps=1e-4, side=4)
 
-CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C}
+# Latent widths in multiples of 16 (the sizes the tensor-core attention kernel takes in bfloat16), with head counts that
+# do not fill its tiles of 16 rows evenly.
+CASE_D = config(128, 263, [
+    (attention(6, 32, 16, 16, 32, 64, base=250000.0), moe(8, 2, 48, shared=32)),
+    (recurrent(160, 5, 4), moe(8, 2, 48, shared=32)),
+    (attention(6, 32, 16, 16, 32, 64, base=250000.0, kv_from=0), None),
+    (attention(20, 16, 32, 32, 16, 128, base=10000.0), moe(8, 2, 48)),
+], mult=0.5, eps=1e-6, side=16)
+
+CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
 
 
 def seeded_state(cfg: dict, seed: int, sharp: float = 1.0, router_gain: float = 4.0) -> dict:

@@ -144,6 +144,63 @@ def test_routed_experts_alone(gpu, experts, top, shared):
     close(out, want, 3e-6)
 
 
+def test_the_router_as_a_product_chooses_as_the_fused_kernel(gpu):
+    from stride_b200.csrc import ops
+    g = torch.Generator().manual_seed(8)
+    tokens, hidden, experts, top = 70, 96, 11, 3
+    x, w, b = torch.randn(tokens, hidden, generator=g).cuda(), torch.randn(experts, hidden, generator=g).cuda(), torch.randn(experts, generator=g).cuda()
+    seq = torch.zeros(tokens, dtype=torch.int32, device="cuda")
+    seq[5] = -1
+    ids1, w1 = torch.empty(tokens, top, dtype=torch.int32, device="cuda"), torch.empty(tokens, top, device="cuda")
+    ids2, w2 = torch.empty_like(ids1), torch.empty_like(w1)
+    ops.moe_route(x, w, b, seq, ids1, w1)
+    logits = torch.empty(tokens, experts, device="cuda")
+    ops.linear(x, w, logits)
+    ops.moe_select(logits, b, seq, ids2, w2)
+    assert torch.equal(ids1, ids2) and (ids1[5] == -1).all()
+    close(w2, w1, 1e-5)
+    z = (x.double() @ w.double().T + b.double()).cpu()
+    assert torch.equal(ids1.cpu().long()[6], z[6].topk(top).indices)
+
+
+@pytest.mark.parametrize("heads,rank,rot,page", [(6, 64, 16, 16), (20, 128, 32, 8), (1, 16, 16, 4)])
+def test_tensor_core_latent_attention_against_the_exact_kernel(gpu, heads, rank, rot, page):
+    """Portions and single tokens of three requests in one step, keys scattered over shuffled pages."""
+    from stride_b200.csrc import ops
+    g = torch.Generator().manual_seed(heads)
+    lens = [(0, 75), (130, 1), (257, 1), (40, 9)]                    # (cached, new): a prompt, two decoded tokens, a portion
+    order = [0, 3, 1, 2]                                              # single tokens last, as the step function lays a batch out
+    lens = [lens[i] for i in order]
+    total_pages = sum(-(-(c + n) // page) for c, n in lens) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    latent = (torch.randn(total_pages, 1, page, rank, generator=g) * 0.7).bfloat16().cuda()
+    key_rot = (torch.randn(total_pages, 1, page, rot, generator=g) * 0.7).bfloat16().cuda()
+    width = max(-(-(c + n) // page) for c, n in lens)
+    table = torch.zeros(len(lens), width, dtype=torch.int32)
+    q_start, q_len, ctx_len, seq_of, positions, at = [], [], [], [], [], 0
+    for s, (c, n) in enumerate(lens):
+        pages = [perm.pop() for _ in range(-(-(c + n) // page))]
+        table[s, :len(pages)] = torch.tensor(pages)
+        q_start.append(at), q_len.append(n), ctx_len.append(c + n)
+        seq_of += [s] * n
+        positions += list(range(c, c + n))
+        at += n
+    tokens = at
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    qa = (torch.randn(tokens, heads * (rank + rot), generator=g) * 0.5).bfloat16().cuda()
+    want, got = torch.zeros(tokens, heads * rank, dtype=torch.bfloat16, device="cuda"), torch.full((tokens, heads * rank), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scale = 0.3
+    ops.latent_attention(qa, want, latent, key_rot, table.cuda(), dev(seq_of), dev(positions), heads, rank, rot, page, scale)
+    args = (latent, key_rot, table.cuda(), dev(q_start), dev(q_len), dev(ctx_len), dev(seq_of))
+    ops.latent_attention_tc(qa, got, None, *args, 0, 2, 0, 84, 75, heads, rank, rot, page, scale)
+    splits, per_split = 3, 128
+    partial = torch.full((tokens * heads * splits * (rank + 2),), float("nan"), device="cuda")
+    ops.latent_attention_tc(qa, got, partial, *args, 2, 2, 84, 2, 1, heads, rank, rot, page, scale, splits=splits, keys_per_split=per_split)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    close(got, want, 2e-2)
+
+
 # ----------------------------------------------------------- each mixer alone, in a model of nothing else
 ONLY_RECURRENT = cases.config(72, 101, [(cases.recurrent(88, 4, 5), None), (cases.recurrent(40, 1, 2), None)], mult=1.0)
 ONLY_ATTENTION = cases.config(72, 101, [(cases.attention(3, 24, 8, 4, 16, 48), None),
@@ -161,7 +218,7 @@ def test_each_mechanism_in_a_model_of_its_own(gpu, tmp_models, name, cfg):
 
 # ---------------------------------------------------------------------------- whole models, every cutting
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case,page", [("A", 16), ("B", 8), ("C", 32)])
+@pytest.mark.parametrize("case,page", [("A", 16), ("B", 8), ("C", 32), ("D", 16)])
 def test_every_cutting_gives_the_plain_logits(gpu, tmp_models, case, page, dtype):
     cfg = cases.CASES[case]
     folder, requests, want = model_case(tmp_models, case, cfg, dtype, 11, [70, 33, 1, 52, 9, 2])
