@@ -42,47 +42,82 @@ __device__ __forceinline__ void mma_tile_64x64(TileSmem& sm, const __nv_bfloat16
         for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
-    for (int k0 = 0; k0 < K; k0 += TK) {
-        // A: 64 rows x 4 chunks of 8 elements
-        for (int c = tid; c < TM * 4; c += 128) {
+    // Each thread fetches two 16-byte pieces of A and two of B a step (or 16 single elements of B where n is the
+    // contiguous index). The pieces of step k + 1 are requested into registers before the products of step k run,
+    // so the latency of global memory is covered by arithmetic.
+    uint4 pa[2], pb[2];
+    __nv_bfloat16 pbs[(TN * TK) / 128];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int c = tid + x * 128;
             const int r = c >> 2, kc = (c & 3) * 8;
             const __nv_bfloat16* src = sm.a_rows[r];
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (src) {
+            if (src && k0 + kc < K) {
                 src += k0 + kc;
                 if (k0 + kc + 8 <= K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
                     v = *reinterpret_cast<const uint4*>(src);
                 } else {
                     __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
-                    for (int x = 0; x < 8; ++x)
-                        if (k0 + kc + x < K) e[x] = src[x];
+                    for (int y = 0; y < 8; ++y)
+                        if (k0 + kc + y < K) e[y] = src[y];
                 }
             }
-            *reinterpret_cast<uint4*>(&sm.a[r][kc]) = v;
+            pa[x] = v;
         }
         if (b_ks == 1) {
-            for (int c = tid; c < TN * 4; c += 128) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const int c = tid + x * 128;
                 const int n = c >> 2, kc = (c & 3) * 8;
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (n0 + n < N) {
+                if (n0 + n < N && k0 + kc < K) {
                     const __nv_bfloat16* src = B + static_cast<long long>(n0 + n) * b_ns + k0 + kc;
                     if (k0 + kc + 8 <= K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
                         v = *reinterpret_cast<const uint4*>(src);
                     } else {
                         __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
-                        for (int x = 0; x < 8; ++x)
-                            if (k0 + kc + x < K) e[x] = src[x];
+                        for (int y = 0; y < 8; ++y)
+                            if (k0 + kc + y < K) e[y] = src[y];
                     }
                 }
-                *reinterpret_cast<uint4*>(&sm.b[n][kc]) = v;
+                pb[x] = v;
             }
         } else {        // n contiguous in memory: neighbouring threads read neighbouring n
-            for (int c = tid; c < TN * TK; c += 128) {
+#pragma unroll
+            for (int x = 0; x < (TN * TK) / 128; ++x) {
+                const int c = tid + x * 128;
                 const int k = c / TN, n = c % TN;
-                sm.b[n][k] = (n0 + n < N && k0 + k < K) ? B[static_cast<long long>(n0 + n) * b_ns + static_cast<long long>(k0 + k) * b_ks]
-                                                        : __float2bfloat16_rn(0.f);
+                pbs[x] = (n0 + n < N && k0 + k < K) ? B[static_cast<long long>(n0 + n) * b_ns + static_cast<long long>(k0 + k) * b_ks]
+                                                    : __float2bfloat16_rn(0.f);
             }
         }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int c = tid + x * 128;
+            *reinterpret_cast<uint4*>(&sm.a[c >> 2][(c & 3) * 8]) = pa[x];
+        }
+        if (b_ks == 1) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const int c = tid + x * 128;
+                *reinterpret_cast<uint4*>(&sm.b[c >> 2][(c & 3) * 8]) = pb[x];
+            }
+        } else {
+#pragma unroll
+            for (int x = 0; x < (TN * TK) / 128; ++x) {
+                const int c = tid + x * 128;
+                sm.b[c % TN][c / TN] = pbs[x];
+            }
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += TK) {
+        stash();
+        if (k0 + TK < K) fetch(k0 + TK);
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < TK; kk += 16) {

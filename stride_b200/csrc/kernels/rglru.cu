@@ -121,11 +121,28 @@ rglru_scan_kernel(const float* __restrict__ a /* a - 1 */, const float* __restri
     float* rows = state + static_cast<size_t>(state_slot[seq]) * taps * width;
     float s = rows[static_cast<size_t>(taps - 1) * width + c];
     const float by = bias_y[c];
-    // nothing the loop loads depends on s: unrolled, eight tokens' loads are in flight while the chain of s runs
-#pragma unroll 8
-    for (int i = 0; i < n; ++i) {
+    // Nothing the loop loads depends on s: eight tokens' values are fetched into registers before the chain of s runs
+    // over them, so their latencies overlap. The order of the arithmetic is the token order either way.
+    constexpr int AHEAD = 8;
+    int i = 0;
+    for (; i + AHEAD <= n; i += AHEAD) {
+        float am1[AHEAD], g[AHEAD], yp[AHEAD];
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            const size_t at = static_cast<size_t>(start + i + j) * width + c;
+            am1[j] = a[at];
+            g[j] = gx[at];
+            yp[j] = to_f32(xy[static_cast<size_t>(start + i + j) * ld + y_off + c]);
+        }
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            s = fmaf(am1[j], s, s) + g[j];      // a S + gx with a - 1 stored
+            out[static_cast<size_t>(start + i + j) * width + c] = from_f32<T>(s * gelu_tanh_f(yp[j] + by));
+        }
+    }
+    for (; i < n; ++i) {
         const size_t at = static_cast<size_t>(start + i) * width + c;
-        s = fmaf(a[at], s, s) + gx[at];         // a S + gx with a - 1 stored
+        s = fmaf(a[at], s, s) + gx[at];
         const float y = gelu_tanh_f(to_f32(xy[static_cast<size_t>(start + i) * ld + y_off + c]) + by);
         out[at] = from_f32<T>(s * y);
     }
