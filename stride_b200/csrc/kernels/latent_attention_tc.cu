@@ -34,6 +34,14 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
 
+// 16 bytes from global to shared memory without a register in between; `bytes` 0 writes zeros. Many of them are in
+// flight per thread, which is what makes a tile of scattered rows arrive in one memory latency and not in one a row.
+__device__ __forceinline__ void copy16_async(void* smem_dst, const void* src, int bytes) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copies_done() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -81,9 +89,8 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
     const size_t first_global_row = static_cast<size_t>(start) * heads + r0;
     for (int c = tid; c < ROWS * chunks; c += NW * 32) {
         const int r = c / chunks, x = (c % chunks) * 8;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r0 + r < total_rows) v = *reinterpret_cast<const uint4*>(qa + (first_global_row + r) * width + x);
-        *reinterpret_cast<uint4*>(Qs + r * ld + x) = v;
+        const bool live = r0 + r < total_rows;
+        copy16_async(Qs + r * ld + x, qa + (first_global_row + (live ? r : 0)) * width + x, live ? 16 : 0);
     }
     const int32_t* table = block_table + static_cast<size_t>(seq) * table_width;
     const int ntiles = rank / 8;
@@ -111,15 +118,12 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
         // ---- the key tile: [latent | rotated part] of 64 keys through the block table
         for (int c = tid; c < KT * chunks; c += NW * 32) {
             const int j = c / chunks, x = (c % chunks) * 8;
-            const int key = kt + j;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (key < k_end) {
-                const size_t slot = static_cast<size_t>(table[key / page_size]) * page_size + key % page_size;
-                v = x < rank ? *reinterpret_cast<const uint4*>(latent_pages + slot * rank + x)
-                             : *reinterpret_cast<const uint4*>(krot_pages + slot * rot + (x - rank));
-            }
-            *reinterpret_cast<uint4*>(Ks + j * ld + x) = v;
+            const int key = min(kt + j, k_end - 1);                 // a key beyond the end: zeros, whatever the address
+            const size_t slot = static_cast<size_t>(table[key / page_size]) * page_size + key % page_size;
+            const __nv_bfloat16* src = x < rank ? latent_pages + slot * rank + x : krot_pages + slot * rot + (x - rank);
+            copy16_async(Ks + j * ld + x, src, kt + j < k_end ? 16 : 0);
         }
+        copies_done();
         __syncthreads();
         // ---- S = Q K^T for this warp's keys
         float acc_s[MT][SN][4];
@@ -236,6 +240,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
         __syncthreads();
     }
 
+    copies_done();          // a CTA without keys still has its queries on the way
     // ---- result
 #pragma unroll
     for (int i = 0; i < MT; ++i)

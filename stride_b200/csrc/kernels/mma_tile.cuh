@@ -1,7 +1,7 @@
 // A 64 x 64 output tile of C = A B^T in bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulators), for
 // the small products that sit between the library products of a layer: the per-head products of latent attention
 // and the experts' products, whose rows are scattered or ragged. Four warps, each 32 x 32 of the tile; operands are
-// staged in shared memory 32 columns of K at a time (rows padded to 40 elements: the fragment loads of a warp then fall
+// staged in shared memory 64 columns of K at a time (rows padded by 8 elements: the fragment loads of a warp then fall
 // into 32 different banks) and read as the instruction's fragments with plain 32-bit loads.
 //
 //   A: row r of the tile starts at a_rows[r] (nullptr: the row is beyond the end and counts as zeros), K contiguous.
@@ -14,7 +14,9 @@
 
 namespace stride {
 
-constexpr int TM = 64, TN = 64, TK = 32, TPAD = 40;
+constexpr int TM = 64, TN = 64, TK = 64, TPAD = TK + 8;
+constexpr int TCH = TK / 8;                 // 16-byte pieces a row and step
+constexpr int TPIECES = TM * TCH / 128;     // pieces of A (and of B) a thread and step
 
 struct __align__(16) TileSmem {
     __nv_bfloat16 a[TM][TPAD];
@@ -42,16 +44,16 @@ __device__ __forceinline__ void mma_tile_64x64(TileSmem& sm, const __nv_bfloat16
         for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
-    // Each thread fetches two 16-byte pieces of A and two of B a step (or 16 single elements of B where n is the
+    // Each thread fetches four 16-byte pieces of A and four of B a step (or 16 single elements of B where n is the
     // contiguous index). The pieces of step k + 1 are requested into registers before the products of step k run,
     // so the latency of global memory is covered by arithmetic.
-    uint4 pa[2], pb[2];
+    uint4 pa[TPIECES], pb[TPIECES];
     __nv_bfloat16 pbs[(TN * TK) / 128];
     auto fetch = [&](int k0) {
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
+        for (int x = 0; x < TPIECES; ++x) {
             const int c = tid + x * 128;
-            const int r = c >> 2, kc = (c & 3) * 8;
+            const int r = c / TCH, kc = (c % TCH) * 8;
             const __nv_bfloat16* src = sm.a_rows[r];
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (src && k0 + kc < K) {
@@ -68,9 +70,9 @@ __device__ __forceinline__ void mma_tile_64x64(TileSmem& sm, const __nv_bfloat16
         }
         if (b_ks == 1) {
 #pragma unroll
-            for (int x = 0; x < 2; ++x) {
+            for (int x = 0; x < TPIECES; ++x) {
                 const int c = tid + x * 128;
-                const int n = c >> 2, kc = (c & 3) * 8;
+                const int n = c / TCH, kc = (c % TCH) * 8;
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
                 if (n0 + n < N && k0 + kc < K) {
                     const __nv_bfloat16* src = B + static_cast<long long>(n0 + n) * b_ns + k0 + kc;
@@ -96,15 +98,15 @@ __device__ __forceinline__ void mma_tile_64x64(TileSmem& sm, const __nv_bfloat16
     };
     auto stash = [&]() {
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
+        for (int x = 0; x < TPIECES; ++x) {
             const int c = tid + x * 128;
-            *reinterpret_cast<uint4*>(&sm.a[c >> 2][(c & 3) * 8]) = pa[x];
+            *reinterpret_cast<uint4*>(&sm.a[c / TCH][(c % TCH) * 8]) = pa[x];
         }
         if (b_ks == 1) {
 #pragma unroll
-            for (int x = 0; x < 2; ++x) {
+            for (int x = 0; x < TPIECES; ++x) {
                 const int c = tid + x * 128;
-                *reinterpret_cast<uint4*>(&sm.b[c >> 2][(c & 3) * 8]) = pb[x];
+                *reinterpret_cast<uint4*>(&sm.b[c / TCH][(c % TCH) * 8]) = pb[x];
             }
         } else {
 #pragma unroll

@@ -82,6 +82,7 @@ rglru_gates_kernel(const float* __restrict__ u, const T* __restrict__ wa_t, cons
     for (int tt = 0; tt < GT; ++tt) accr[tt] = acci[tt] = 0.f;
     const T* wa = wa_t + static_cast<size_t>(b) * bw * bw + oc;
     const T* wi = wi_t + static_cast<size_t>(b) * bw * bw + oc;
+#pragma unroll 4
     for (int k = 0; k < bw; ++k) {
         const float wr = to_f32(wa[static_cast<size_t>(k) * bw]), wg = to_f32(wi[static_cast<size_t>(k) * bw]);
 #pragma unroll
