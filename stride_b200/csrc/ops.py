@@ -102,6 +102,8 @@ _SIGNATURES = {
                                      c_int, c_int, c_void_p]),
     "stride_rglru_scan": ("rglru", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_rglru_scan_pieces": ("rglru", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_moe_route": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_moe_plan": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "stride_grouped_gemm": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -137,7 +139,7 @@ _CLASS_OF = {
     "stride_latent_attention": "attention (latent, exact kernel)", "stride_latent_attention_tc": "attention (latent, tensor cores)",
     "stride_side_gate": "token side input", "stride_side_norm_add": "token side input", "stride_cast_rows": "token side input",
     "stride_moe_select": "router", "stride_rglru_conv": "recurrent block: convolution",
-    "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_moe_route": "router",
+    "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_rglru_scan_pieces": "recurrent block: recurrence", "stride_moe_route": "router",
     "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
     "stride_relu_squared": "relu^2",
 }
@@ -453,6 +455,24 @@ def rglru_scan(a, gx, xy, x_off: int, y_off: int, bias_x, bias_y, state, q_start
                                     _dev(state, "state", torch.float32), _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
                                     _dev(state_slot, "state_slot", torch.int32), _dev(out, "out"), num_seqs, width, taps,
                                     _code(out.dtype), _stream()), "rglru_scan")
+
+
+SCAN_PIECES_MIN_TOKENS = int(_os.environ.get("STRIDE_B200_SCAN_PIECES_MIN", "256"))
+
+
+def rglru_scan_pieces(a, gx, xy, x_off: int, y_off: int, bias_x, bias_y, state, q_start, q_len, state_slot, out, piece, num_seqs: int,
+                      max_q_len: int, taps: int) -> None:
+    """``rglru_scan`` in three passes over pieces of 64 tokens, parallel over the pieces (bfloat16 activations). ``piece``:
+    float32 scratch of at least ``(tokens // 64 + num_seqs + 1) * 2 * width``."""
+    width = out.shape[1]
+    if piece.numel() < (out.shape[0] // 64 + num_seqs + 1) * 2 * width:
+        raise KernelError("rglru_scan_pieces: the scratch is too small")
+    _check(_fn("stride_rglru_scan_pieces")(
+        _dev(a, "a", torch.float32), _dev(gx, "gx", torch.float32), _dev(xy, "xy", torch.bfloat16), xy.shape[1], int(x_off), int(y_off),
+        _dev(bias_x, "bias_x", torch.float32), _dev(bias_y, "bias_y", torch.float32), _dev(state, "state", torch.float32),
+        _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32),
+        _dev(out, "out", torch.bfloat16), _dev(piece, "piece", torch.float32), num_seqs, max_q_len, width, taps, _code(out.dtype), _stream()),
+        "rglru_scan_pieces")
 
 
 # ------------------------------------------------------------------ routed experts

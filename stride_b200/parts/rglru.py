@@ -8,7 +8,10 @@ equal parts of the channels, ``r = sigmoid(W_a u + b_a)`` and ``i = sigmoid(W_i 
 
 Per request the mixer keeps, in one state slot of shape [taps, width] float32, the last taps-1 inputs of the
 convolution (oldest first) and S (last row). The framework hands the slot out and clears it when a request starts;
-the kernels read the step from its device arrays, so a decode step can be replayed from a graph.
+the kernels read the step from its device arrays, so a decode step can be replayed from a graph. In bfloat16 a
+portion of 256 tokens or more runs the recurrence in pieces of 64 tokens (the map of a piece, S -> P S + B, first; then
+the states at the pieces' starts; then every piece from its start), parallel over the pieces; the 32-bit path and short
+steps keep the one chain in token order.
 
 Spec params: ``width``, ``blocks``, ``taps``, ``decay_scale``. Tensors under the prefix: ``y``, ``y.b``, ``x``, ``x.b``,
 ``conv`` [width, taps] (the last column weighs the current token), ``conv.b``, ``ra`` / ``ri`` [blocks, out, in],
@@ -81,8 +84,15 @@ class RecurrentGatedUnit(Mixer):
         gx = self.rt.buffer("rglru_gx", tokens, w, torch.float32)
         ops.rglru_gates(u, self.wa_t, self.wi_t, self.ba, self.bi, self.lam, self.decay, a, gx, self.blocks)
         mixed = self.rt.buffer("rglru_out", tokens, w)
-        ops.rglru_scan(a, gx, xy, w, 0, self.bias_x, self.bias_y, cache.state, ctx.q_start, ctx.q_len, ctx.state_slot, mixed,
-                       ctx.q_len.shape[0], self.taps)
+        seqs = ctx.q_len.shape[0]
+        if x.dtype == torch.bfloat16 and ctx.max_q_len >= ops.SCAN_PIECES_MIN_TOKENS:
+            # a long portion: the recurrence in pieces of 64 tokens, parallel over the pieces
+            piece = self.rt.scratch("rglru_pieces", (tokens // 64 + seqs + 1) * 2 * w)
+            ops.rglru_scan_pieces(a, gx, xy, w, 0, self.bias_x, self.bias_y, cache.state, ctx.q_start, ctx.q_len, ctx.state_slot, mixed,
+                                  piece, seqs, ctx.max_q_len, self.taps)
+        else:
+            ops.rglru_scan(a, gx, xy, w, 0, self.bias_x, self.bias_y, cache.state, ctx.q_start, ctx.q_len, ctx.state_slot, mixed,
+                           seqs, self.taps)
         if lazy_output:
             return Projection(mixed, self.w_o)
         out = self.rt.buffer("mixer_out", tokens, self.hidden)

@@ -285,6 +285,20 @@ def test_a_far_key_that_stands_out_is_found(gpu, tmp_models):
     replay(folder, "float32", modes.changing_portions(requests, sizes=(4, 5, 3, 31, 2)), want, 4, 1, "far portions")
 
 
+def test_the_recurrence_in_pieces_gives_the_chain(gpu, tmp_models, monkeypatch):
+    """bfloat16, prompts long enough for the piecewise scan (and a batch of two of them with a short one between):
+    against the plain chain, and against the engine's own token-order kernel."""
+    from stride_b200.csrc import ops
+    cfg = cases.config(64, 101, [(cases.recurrent(96, 3, 4), None), (cases.recurrent(64, 1, 2), cases.moe(4, 2, 24))], mult=0.5, side=8)
+    folder, requests, want = model_case(tmp_models, "pieces", cfg, "bfloat16", 31, [300, 70, 261])
+    monkeypatch.setattr(ops, "SCAN_PIECES_MIN_TOKENS", 128)
+    together = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": [0, len(t) // 2, len(t) - 1]} for r, t in requests.items()],
+                 "end": list(requests)}]
+    replay(folder, "bfloat16", together, want, 16, 3, "three prompts in one step", min_ok=0.97)
+    steps = modes.restrict_wants(modes.changing_portions(requests, sizes=(130, 2, 140, 65)), {r: set(range(0, len(t), 5)) for r, t in requests.items()})
+    replay(folder, "bfloat16", steps, want, 16, 3, "portions across the pieces' borders", min_ok=0.97)
+
+
 # --------------------------------------------------------------------------- generation through the engine
 def test_greedy_generation_through_the_engine(gpu, tmp_models):
     from stride_b200 import Engine, SamplingParams
