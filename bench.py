@@ -380,7 +380,14 @@ def run_profile(args) -> dict:
 
     from stride_b200 import Engine
 
-    cfg, full_layers = bench_config(args.layers, args.shape)
+    if args.compare:        # the compared design at the first of --compare-sizes instead of a Llama shape
+        from stride_b200.config import config_from_dict
+        full_layers = args.layers or 6
+        cfg = config_from_dict(compare_configs(COMPARE_SIZES[args.compare_sizes.split(",")[0]], full_layers)[0])
+        vocab, layers = cfg.vocab, full_layers
+    else:
+        cfg, full_layers = bench_config(args.layers, args.shape)
+        vocab, layers = cfg.vocab_size, cfg.num_hidden_layers
     batch, context = args.batch, args.context
     engine = Engine(config=cfg, random_weights=0, dtype="bfloat16", block_size=16,
                     num_blocks=(batch * (context + 64) + 4096) // 16, max_batch_tokens=2048, max_batch_seqs=64,
@@ -394,11 +401,11 @@ def run_profile(args) -> dict:
         engine.cache.open(1, "bench")
         engine.cache.ensure(1, 2048, 0)
         step_batch = engine._rt.StepBatch(engine.cache)
-        step_batch.add(1, torch.randint(0, cfg.vocab_size, (2048,), generator=g).tolist(), 0, [2047])
+        step_batch.add(1, torch.randint(0, vocab, (2048,), generator=g).tolist(), 0, [2047])
     for _ in range(args.warmup + args.steps):
         engine.runner.step(step_batch)
     torch.cuda.synchronize()
-    return {"profiled": args.profile, "layers": cfg.num_hidden_layers, "layers_of_named_config": full_layers, "batch": batch,
+    return {"profiled": args.profile, "layers": layers, "layers_of_named_config": full_layers, "batch": batch,
             "context": context, "steps": args.warmup + args.steps}
 
 

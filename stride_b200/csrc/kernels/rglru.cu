@@ -126,6 +126,56 @@ rglru_gates_kernel(const float* __restrict__ u, const T* __restrict__ wa_t, cons
     }
 }
 
+// The same products for a long step: GT tokens x 128 output channels of one block a CTA, each thread one channel and
+// the whole sum over the block's inputs; the tokens' inputs lie [input][token] in shared memory, so that a thread takes
+// the eight tokens of an input with two 16-byte loads for sixteen multiply-adds.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rglru_gates_wide_kernel(const float* __restrict__ u, const T* __restrict__ wa_t, const T* __restrict__ wi_t, const float* __restrict__ ba,
+                        const float* __restrict__ bi, const float* __restrict__ lam, float decay, float* __restrict__ a_out,
+                        float* __restrict__ gx_out, int tokens, int width, int bw) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float us[];         // [bw][GT]
+    const int b = blockIdx.y;
+    const int t0 = blockIdx.z * GT;
+    const int oc = blockIdx.x * 128 + threadIdx.x;
+    for (int i = threadIdx.x; i < GT * bw; i += 128) {
+        const int tt = i / bw, k = i % bw;
+        us[k * GT + tt] = t0 + tt < tokens ? u[static_cast<size_t>(t0 + tt) * width + b * bw + k] : 0.f;
+    }
+    __syncthreads();
+    if (oc >= bw) return;
+    float accr[GT], acci[GT];
+#pragma unroll
+    for (int tt = 0; tt < GT; ++tt) accr[tt] = acci[tt] = 0.f;
+    const T* wa = wa_t + static_cast<size_t>(b) * bw * bw + oc;
+    const T* wi = wi_t + static_cast<size_t>(b) * bw * bw + oc;
+#pragma unroll 4
+    for (int k = 0; k < bw; ++k) {
+        const float wr = to_f32(wa[static_cast<size_t>(k) * bw]), wg = to_f32(wi[static_cast<size_t>(k) * bw]);
+        const float4 x0 = *reinterpret_cast<const float4*>(us + k * GT), x1 = *reinterpret_cast<const float4*>(us + k * GT + 4);
+        const float x[GT] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int tt = 0; tt < GT; ++tt) {
+            accr[tt] = fmaf(wr, x[tt], accr[tt]);
+            acci[tt] = fmaf(wg, x[tt], acci[tt]);
+        }
+    }
+    const int c = b * bw + oc;
+    const float rate = decay * softplus_f(lam[c]);
+    const float br = ba[c], bg = bi[c];
+#pragma unroll
+    for (int tt = 0; tt < GT; ++tt) {
+        if (t0 + tt >= tokens) break;
+        const float r = sigmoid_f(accr[tt] + br), g = sigmoid_f(acci[tt] + bg);
+        const float log_a = -rate * r;
+        const size_t at = static_cast<size_t>(t0 + tt) * width + c;
+        a_out[at] = expm1f(log_a);
+        gx_out[at] = sqrtf(-expm1f(2.f * log_a)) * g * us[oc * GT + tt];
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(64)
 rglru_scan_kernel(const float* __restrict__ a /* a - 1 */, const float* __restrict__ gx, const T* __restrict__ xy, int ld, int x_off, int y_off,
@@ -299,6 +349,15 @@ int stride_rglru_gates(const float* u, const void* wa_t, const void* wi_t, const
     if (smem > 48 * 1024) return STRIDE_UNSUPPORTED;
     const dim3 grid((bw + GC - 1) / GC, blocks, (tokens + GT - 1) / GT);
     if (grid.z > 65535 || grid.y > 65535) return STRIDE_UNSUPPORTED;
+    if (tokens > 64 && dtype == STRIDE_DTYPE_BF16) {
+        // Long steps in bfloat16 mode: one thread sums all of a block's inputs. (The 32-bit path keeps one form for
+        // every step, so that a token's sums have the same order however the step was cut.)
+        const dim3 wide((bw + 127) / 128, blocks, (tokens + GT - 1) / GT);
+        stride::launch(rglru_gates_wide_kernel<__nv_bfloat16>, wide, dim3(128), static_cast<size_t>(GT) * bw * sizeof(float), stream, u,
+                       static_cast<const __nv_bfloat16*>(wa_t), static_cast<const __nv_bfloat16*>(wi_t), ba, bi, lam, decay, a_out, gx_out,
+                       tokens, width, bw);
+        return STRIDE_LAUNCH_STATUS();
+    }
     if (dtype == STRIDE_DTYPE_F32)
         stride::launch(rglru_gates_kernel<float>, grid, dim3(GC * GS), smem, stream, u, static_cast<const float*>(wa_t),
                        static_cast<const float*>(wi_t), ba, bi, lam, decay, a_out, gx_out, tokens, width, bw);
