@@ -1,4 +1,4 @@
-"""Named Llama 3 shapes, as config.json dictionaries: the tiny shapes used
+"""Named shapes, as config.json dictionaries (Llama 3, and two of the Nidilix design): the tiny shapes used
 for correctness runs (tiny-d has the head size and widths that the tensor-core
 kernels take) and the 8B / 3B / 70B shapes used for measurements. The
 reference keeps such presets in crates/stride-model/src/presets.rs:73-91."""
@@ -23,7 +23,35 @@ def _llama(layers, hidden, heads, kv_heads, head_dim, inter, vocab, theta, scali
     return d
 
 
+def _nidilix(width, vocab, pattern, recurrent, attention, mlp, side, mult=0.5, eps=1e-6) -> dict:
+    """``pattern``: a string of ``r`` (recurrent layer), ``a`` (latent attention with a cache of its own) and ``b`` (latent
+    attention that reads the cache of the nearest ``a`` before it)."""
+    layers, last = [], None
+    for i, kind in enumerate(pattern):
+        if kind == "r":
+            layers.append({"type": "rglru", "mixer": dict(recurrent), "mlp": copy.deepcopy(mlp)})
+            continue
+        mixer = copy.deepcopy(attention)
+        if kind == "b":
+            mixer["kv_from"] = last
+        else:
+            last = i
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": copy.deepcopy(mlp)})
+    d = {"architecture": "Nidilix", "width": width, "vocab": vocab, "residual_mult": mult, "norm": {"eps": eps}, "layers": layers}
+    if side:
+        d["token_side"] = {"dim": side}
+    return d
+
+
 PRESETS = {
+    "nidilix-tiny": _nidilix(128, 512, "rarb", {"width": 160, "blocks": 4, "conv": 4},
+                             {"heads": 4, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "rot": {"base": 10000.0, "dims": 16},
+                              "scale": 48 ** -0.5},
+                             {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 64}, "shared": {"ff": 64}}, 16),
+    "nidilix-2048": _nidilix(2048, 32000, "rrarrb", {"width": 2560, "blocks": 10, "conv": 4},
+                             {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "rot": {"base": 10000.0, "dims": 64},
+                              "scale": 192 ** -0.5},
+                             {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 768}, "shared": {"ff": 1024}}, 128),
     "tiny-a": _llama(2, 64, 4, 2, 16, 192, 256, 10000.0, None, 1e-5, False, 256),
     "tiny-b": _llama(3, 96, 3, 1, 32, 256, 384, 500000.0, _llama3_scaling(8.0, 64), 1e-6, True, 512),
     "tiny-d": _llama(2, 192, 4, 2, 128, 384, 515, 500000.0, _llama3_scaling(8.0, 128), 1e-5, False, 2048),

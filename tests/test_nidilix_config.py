@@ -77,3 +77,12 @@ def test_a_model_folder_is_written_and_read_back(tmp_path):
     assert again == cfg
     check_source(source, _declarations(again), ())
     assert source.describe("l0.norm1.alpha")[0] == ()
+
+
+def test_presets_of_the_design_parse_and_plan():
+    from stride_b200.config import config_from_dict, plan_memory, preset
+    tiny = config_from_dict(preset("nidilix-tiny"))
+    assert [l["type"] for l in tiny.layers] == ["rglru", "latent_attention", "rglru", "latent_attention"] and tiny.layers[3]["mixer"]["kv_from"] == 1
+    big = config_from_dict(preset("nidilix-2048"))
+    plan = plan_memory(big, "bfloat16", 180 * (1 << 30), 16, 0.15, name="nidilix-2048")
+    assert plan.concurrent_sequences(8192) > 0
