@@ -44,10 +44,10 @@ def _nidilix(width, vocab, pattern, recurrent, attention, mlp, side, mult=0.5, e
 
 
 PRESETS = {
-    "nidilix-tiny": _nidilix(128, 512, "rarb", {"width": 160, "blocks": 4, "conv": 4},
-                             {"heads": 4, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "rot": {"base": 10000.0, "dims": 16},
-                              "scale": 48 ** -0.5},
-                             {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 64}, "shared": {"ff": 64}}, 16),
+    "nidilix-tiny": _nidilix(128, 512, "rarb", {"width": 160, "blocks": 5, "conv": 3},
+                             {"heads": 4, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": 48, "rot": {"base": 10000.0, "dims": 16},
+                              "scale": 32 ** -0.5},
+                             {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 64}, "shared": {"ff": 32}}, 8),
     "nidilix-2048": _nidilix(2048, 32000, "rrarrb", {"width": 2560, "blocks": 10, "conv": 4},
                              {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "rot": {"base": 10000.0, "dims": 64},
                               "scale": 192 ** -0.5},

@@ -163,7 +163,7 @@ def test_the_router_as_a_product_chooses_as_the_fused_kernel(gpu):
     assert torch.equal(ids1.cpu().long()[6], z[6].topk(top).indices)
 
 
-@pytest.mark.parametrize("heads,rank,rot,page", [(6, 64, 16, 16), (20, 128, 32, 8), (1, 16, 16, 4)])
+@pytest.mark.parametrize("heads,rank,rot,page", [(6, 80, 16, 16), (20, 128, 32, 8), (1, 16, 16, 4)])
 def test_tensor_core_latent_attention_against_the_exact_kernel(gpu, heads, rank, rot, page):
     """Portions and single tokens of three requests in one step, keys scattered over shuffled pages."""
     from stride_b200.csrc import ops
