@@ -276,7 +276,9 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
         }
 }
 
-// One warp per (token, head): the splits' partial results, combined in the order of the splits.
+// One warp per (token, head): the splits' partial results, combined in the order of the splits. Every lane first takes
+// the weight exp(m_s - m) / L of the splits s = lane and lane + 32 (at most 64 splits), so that the sums over the latent's
+// columns are independent loads and multiply-adds.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ seq_of_token,
                     int first_token, int rows, int heads, int rank, int splits) {
@@ -286,22 +288,30 @@ latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict
     if (r >= rows) return;
     const size_t grow = static_cast<size_t>(first_token) * heads + r;
     if (seq_of_token[first_token + r / heads] < 0) return;
-    const float* src = partial + grow * splits * (rank + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, src[static_cast<size_t>(s) * (rank + 2)]);
+    const size_t stride = static_cast<size_t>(rank) + 2;
+    const float* src = partial + grow * splits * stride;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (lane < splits) { m0 = src[lane * stride]; l0 = src[lane * stride + 1]; }
+    if (lane + 32 < splits) { m1 = src[(lane + 32) * stride]; l1 = src[(lane + 32) * stride + 1]; }
+    const float m = warp_max(fmaxf(m0, m1));
+    float w0 = m0 == -INFINITY ? 0.f : expf(m0 - m), w1 = m1 == -INFINITY ? 0.f : expf(m1 - m);
+    // the sum of the splits' sums in the order of the splits
     float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = src[static_cast<size_t>(s) * (rank + 2)];
-        if (ms != -INFINITY) l += src[static_cast<size_t>(s) * (rank + 2) + 1] * expf(ms - m);
+    for (int s2 = 0; s2 < splits; ++s2) {
+        const float ws = __shfl_sync(0xffffffffu, s2 < 32 ? w0 : w1, s2 & 31), ls = __shfl_sync(0xffffffffu, s2 < 32 ? l0 : l1, s2 & 31);
+        l = fmaf(ls, ws, l);
     }
     const float inv = 1.f / l;
+    w0 *= inv;
+    w1 *= inv;
     for (int d = lane; d < rank; d += 32) {
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = src[static_cast<size_t>(s) * (rank + 2)];
-            if (ms != -INFINITY) acc = fmaf(src[static_cast<size_t>(s) * (rank + 2) + 2 + d], expf(ms - m), acc);
+#pragma unroll 4
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ws = __shfl_sync(0xffffffffu, s2 < 32 ? w0 : w1, s2 & 31);
+            acc = fmaf(src[s2 * stride + 2 + d], ws, acc);
         }
-        out[grow * rank + d] = __float2bfloat16_rn(acc * inv);
+        out[grow * rank + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -334,7 +344,7 @@ int stride_latent_attention_tc(const void* qa, void* out, float* partial, const 
     if (!stride_latent_tc_supported(heads, rank, rot)) return STRIDE_UNSUPPORTED;
     if (splits > 1 && (!partial || keys_per_split <= 0 || keys_per_split % KT)) return STRIDE_BAD_ARGUMENT;
     if (num_seqs == 0 || tokens == 0) return 0;
-    if (num_seqs > 65535 || splits > 65535) return STRIDE_UNSUPPORTED;
+    if (num_seqs > 65535 || splits > 64) return STRIDE_UNSUPPORTED;
     const int kps = splits > 1 ? keys_per_split : 0x3fffffc0;
     const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qa);
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);

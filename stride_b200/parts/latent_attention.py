@@ -155,9 +155,9 @@ class LatentAttention(Mixer):
                                     ctx.decode_tail_seq, 0, split, max(ctx.max_q_len, 2), *geometry)
         if tokens > split:
             n = tokens - split
-            # enough CTAs to fill the device, no split shorter than 256 keys
+            # enough CTAs to fill the device, no split shorter than 128 keys
             tiles = n * -(-self.heads // 16)
-            splits = max(1, min(-(-ctx.context_bound // 256), -(-296 // tiles), 64))
+            splits = max(1, min(-(-ctx.context_bound // 128), -(-296 // tiles), 64))
             per_split = -(-(-(-ctx.context_bound // splits)) // 64) * 64
             splits = max(1, -(-ctx.context_bound // per_split))
             partial = None
