@@ -66,7 +66,16 @@ CASE_D = config(128, 263, [
     (attention(20, 16, 32, 32, 16, 128, base=10000.0), moe(8, 2, 48)),
 ], mult=0.6, eps=2e-6, side=24)
 
-CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
+# Sizes that are multiples of 2 only: rows of 16-bit numbers that start off a 16-byte boundary, so every vector path has
+# to step aside.
+CASE_E = config(100, 103, [
+    (recurrent(60, 3, 2), moe(3, 2, 36, shared=18)),
+    (attention(3, 10, 6, 4, 14, 20, base=4000.0), moe(3, 2, 36, shared=18)),
+    (attention(3, 10, 6, 4, 14, 20, base=4000.0), None),                    # a second cache of the same shape: one group, two slots
+    (attention(3, 10, 6, 4, 14, 20, base=4000.0, kv_from=1), moe(3, 2, 36)),
+], mult=0.8, eps=1e-6, side=6)
+
+CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D, "E": CASE_E}
 
 
 def seeded_state(cfg: dict, seed: int, sharp: float = 1.0, router_gain: float = 4.0) -> dict:

@@ -218,11 +218,15 @@ def test_each_mechanism_in_a_model_of_its_own(gpu, tmp_models, name, cfg):
 
 # ---------------------------------------------------------------------------- whole models, every cutting
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case,page", [("A", 16), ("B", 8), ("C", 32), ("D", 16)])
+@pytest.mark.parametrize("case,page", [("A", 16), ("B", 8), ("C", 32), ("D", 16), ("E", 16)])
 def test_every_cutting_gives_the_plain_logits(gpu, tmp_models, case, page, dtype):
     cfg = cases.CASES[case]
-    folder, requests, want = model_case(tmp_models, case, cfg, dtype, 11, [70, 33, 1, 52, 9, 2])
-    share = 1.0 if dtype == "float32" else 0.97
+    # case E has three experts and takes two: the third logit is often close, so its router is made more decisive
+    folder, requests, want = model_case(tmp_models, case, cfg, dtype, 11, [70, 33, 1, 52, 9, 2], router_gain=16.0 if case == "E" else 4.0)
+    # float32 must agree everywhere. bfloat16: a router's near-tie may fall the other way; and at case E's width of 100
+    # with a multiplier of 0.8 the rounding of single activations reaches the bound on a few rows (its float32 run is exact
+    # to 2e-5, layer by layer)
+    share = 1.0 if dtype == "float32" else (0.9 if case == "E" else 0.97)
     replay(folder, dtype, modes.whole(requests), want, page, 2, "whole", min_ok=share)
     session = replay(folder, dtype, modes.tail_one_by_one(requests, tail=20), want, page, 2, "decode", min_ok=share)
     assert session.runner.graph_replays > 0, "single-token steps did not go through captured graphs"
