@@ -346,7 +346,14 @@ int stride_rglru_gates(const float* u, const void* wa_t, const void* wi_t, const
     if (tokens == 0) return 0;
     const int bw = width / blocks;
     const size_t smem = (static_cast<size_t>(GT) * bw + GS * 2 * GT * GC) * sizeof(float);
-    if (smem > 48 * 1024) return STRIDE_UNSUPPORTED;
+    if (smem > 200 * 1024) return STRIDE_UNSUPPORTED;
+    if (smem > 48 * 1024) {     // blocks of more than 1,280 channels: ask for the shared memory beyond the default limit
+        const int want = static_cast<int>(smem);
+        if (cudaFuncSetAttribute(rglru_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess ||
+            cudaFuncSetAttribute(rglru_gates_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess ||
+            cudaFuncSetAttribute(rglru_gates_wide_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
+            return STRIDE_UNSUPPORTED;
+    }
     const dim3 grid((bw + GC - 1) / GC, blocks, (tokens + GT - 1) / GT);
     if (grid.z > 65535 || grid.y > 65535) return STRIDE_UNSUPPORTED;
     if (tokens > 64 && dtype == STRIDE_DTYPE_BF16) {

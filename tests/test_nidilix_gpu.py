@@ -206,9 +206,11 @@ ONLY_RECURRENT = cases.config(72, 101, [(cases.recurrent(88, 4, 5), None), (case
 ONLY_ATTENTION = cases.config(72, 101, [(cases.attention(3, 24, 8, 4, 16, 48), None),
                                         (cases.attention(3, 24, 8, 4, 16, 48, kv_from=0), None)], mult=0.7)
 ONLY_EXPERTS_AND_SIDE = cases.config(56, 89, [(cases.recurrent(56, 2, 1), cases.moe(6, 3, 20, shared=12))], mult=0.5, side=10)
+ONE_WIDE_BLOCK = cases.config(48, 67, [(cases.recurrent(1536, 1, 3), None)], mult=1.0)       # a block beyond the gates kernel's default shared memory
 
 
-@pytest.mark.parametrize("name,cfg", [("recurrent", ONLY_RECURRENT), ("attention", ONLY_ATTENTION), ("experts", ONLY_EXPERTS_AND_SIDE)])
+@pytest.mark.parametrize("name,cfg", [("recurrent", ONLY_RECURRENT), ("attention", ONLY_ATTENTION), ("experts", ONLY_EXPERTS_AND_SIDE),
+                                      ("wide_block", ONE_WIDE_BLOCK)])
 def test_each_mechanism_in_a_model_of_its_own(gpu, tmp_models, name, cfg):
     folder, requests, want = model_case(tmp_models, name, cfg, "float32", 7, [45, 19, 3])
     replay(folder, "float32", modes.whole(requests), want, 8, 2, name + " whole")
