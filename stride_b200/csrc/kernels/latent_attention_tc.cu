@@ -34,6 +34,16 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
 // 16 bytes from global to shared memory without a register in between; `bytes` 0 writes zeros. Many of them are in
 // flight per thread, which is what makes a tile of scattered rows arrive in one memory latency and not in one a row.
 __device__ __forceinline__ void copy16_async(void* smem_dst, const void* src, int bytes) {
@@ -134,21 +144,16 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc_s[i][j][e] = 0.f;
         for (int kk = 0; kk < width; kk += 16) {
+            // fragments by ldmatrix: a key tile's rows are keys with the K dimension along them, which is the layout of
+            // the B operand as it stands (matrices: keys 0-7 x k 0-7, keys 0-7 x k 8-15)
             uint32_t bf[SN][2];
 #pragma unroll
-            for (int j = 0; j < SN; ++j) {
-                const __nv_bfloat16* kr = Ks + (warp * KW + j * 8 + g) * ld + kk + 2 * t;
-                bf[j][0] = *reinterpret_cast<const uint32_t*>(kr);
-                bf[j][1] = *reinterpret_cast<const uint32_t*>(kr + 8);
-            }
+            for (int j = 0; j < SN; ++j)
+                ldmatrix_x2(bf[j][0], bf[j][1], Ks + (warp * KW + j * 8 + (lane & 7)) * ld + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
                 uint32_t af[4];
-                const __nv_bfloat16* qr = Qs + (i * 16 + g) * ld + kk + 2 * t;
-                af[0] = *reinterpret_cast<const uint32_t*>(qr);
-                af[1] = *reinterpret_cast<const uint32_t*>(qr + 8 * ld);
-                af[2] = *reinterpret_cast<const uint32_t*>(qr + 8);
-                af[3] = *reinterpret_cast<const uint32_t*>(qr + 8 * ld + 8);
+                ldmatrix_x4(af, Qs + (i * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
 #pragma unroll
                 for (int j = 0; j < SN; ++j) mma16816(acc_s[i][j], af, bf[j][0], bf[j][1]);
             }
@@ -219,13 +224,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
         for (int ks = 0; ks < KT; ks += 16) {
             uint32_t af[MT][4];
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                const __nv_bfloat16* pr = Ps + (i * 16 + g) * (KT + 8) + ks + 2 * t;
-                af[i][0] = *reinterpret_cast<const uint32_t*>(pr);
-                af[i][1] = *reinterpret_cast<const uint32_t*>(pr + 8 * (KT + 8));
-                af[i][2] = *reinterpret_cast<const uint32_t*>(pr + 8);
-                af[i][3] = *reinterpret_cast<const uint32_t*>(pr + 8 * (KT + 8) + 8);
-            }
+            for (int i = 0; i < MT; ++i) ldmatrix_x4(af[i], Ps + (i * 16 + (lane & 15)) * (KT + 8) + ks + (lane >> 4) * 8);
 #pragma unroll
             for (int j = 0; j < MAXT; ++j) {
                 const int tile = warp + j * NW;

@@ -2,7 +2,7 @@
 // the small products that sit between the library products of a layer: the per-head products of latent attention
 // and the experts' products, whose rows are scattered or ragged. Four warps, each 32 x 32 of the tile; operands are
 // staged in shared memory 64 columns of K at a time (rows padded by 8 elements: the fragment loads of a warp then fall
-// into 32 different banks) and read as the instruction's fragments with plain 32-bit loads.
+// into 32 different banks) and read as the instruction's fragments with ldmatrix.
 //
 //   A: row r of the tile starts at a_rows[r] (nullptr: the row is beyond the end and counts as zeros), K contiguous.
 //   B: element (n, k) at B[n * b_ns + k * b_ks]; either stride may be 1.
@@ -29,6 +29,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// Four 8 x 8 matrices of 16-bit numbers from shared memory, one row address a lane: lanes 0-7 name the rows of the first
+// matrix, 8-15 of the second, and so on; register k of a lane holds its two elements of matrix k.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
 // acc[i][j][.]: the warp's m16 tile i (rows wm * 32 + i * 16 ..) and n8 tile j (columns wn * 32 + j * 8 ..), wm = warp / 2,
@@ -124,19 +132,18 @@ __device__ __forceinline__ void mma_tile_64x64(TileSmem& sm, const __nv_bfloat16
 #pragma unroll
         for (int kk = 0; kk < TK; kk += 16) {
             uint32_t af[2][4], bf[4][2];
+            // A: rows (lane % 16) of the m16 tile, columns kk + 8 * (lane / 16): the four matrices are the fragment's a0..a3
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int r = wm * 32 + i * 16 + g;
-                af[i][0] = *reinterpret_cast<const uint32_t*>(&sm.a[r][kk + 2 * t]);
-                af[i][1] = *reinterpret_cast<const uint32_t*>(&sm.a[r + 8][kk + 2 * t]);
-                af[i][2] = *reinterpret_cast<const uint32_t*>(&sm.a[r][kk + 2 * t + 8]);
-                af[i][3] = *reinterpret_cast<const uint32_t*>(&sm.a[r + 8][kk + 2 * t + 8]);
-            }
+            for (int i = 0; i < 2; ++i) ldmatrix_x4(af[i], &sm.a[wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+            // B: two n8 tiles a load: matrices (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int n = wn * 32 + j * 8 + g;
-                bf[j][0] = *reinterpret_cast<const uint32_t*>(&sm.b[n][kk + 2 * t]);
-                bf[j][1] = *reinterpret_cast<const uint32_t*>(&sm.b[n][kk + 2 * t + 8]);
+            for (int j = 0; j < 4; j += 2) {
+                uint32_t r[4];
+                ldmatrix_x4(r, &sm.b[wn * 32 + j * 8 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+                bf[j][0] = r[0];
+                bf[j][1] = r[1];
+                bf[j + 1][0] = r[2];
+                bf[j + 1][1] = r[3];
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i)
