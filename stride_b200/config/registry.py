@@ -60,16 +60,21 @@ def config_class_of(d: dict) -> type:
     raise ConfigError(f"none of {names} is supported; registered: {registered_architectures()}")
 
 
-def config_from_dict(d: dict, tensor_names=None):
+def config_from_dict(d: dict, tensor_names=None, tensor_shapes=None):
     """The typed configuration of ``d``. With ``tensor_names`` (what the checkpoint holds) the class may first
-    settle keys that config.json leaves out."""
+    settle keys that config.json leaves out; a class whose ``complete_from_checkpoint`` takes a third argument also
+    gets ``tensor_shapes`` (name -> shape), for sizes that only a tensor's shape gives."""
     cls = config_class_of(d)
     if tensor_names is not None and hasattr(cls, "complete_from_checkpoint"):
-        d = cls.complete_from_checkpoint(dict(d), set(tensor_names))
+        import inspect
+        if tensor_shapes is not None and len(inspect.signature(cls.complete_from_checkpoint).parameters) >= 3:
+            d = cls.complete_from_checkpoint(dict(d), set(tensor_names), dict(tensor_shapes))
+        else:
+            d = cls.complete_from_checkpoint(dict(d), set(tensor_names))
     return cls.from_dict(d)
 
 
-def load_config(model_dir: str, tensor_names=None):
+def load_config(model_dir: str, tensor_names=None, tensor_shapes=None):
     path = os.path.join(model_dir, "config.json")
     try:
         with open(path) as f:
@@ -80,4 +85,4 @@ def load_config(model_dir: str, tensor_names=None):
         raise ConfigError(f"{path} is not valid JSON: {e}") from None
     if not isinstance(d, dict):
         raise ConfigError(f"{path} must hold a JSON object")
-    return config_from_dict(d, tensor_names)
+    return config_from_dict(d, tensor_names, tensor_shapes)

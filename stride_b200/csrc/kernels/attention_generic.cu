@@ -11,6 +11,10 @@
 // with an online softmax, so the order of every sum depends only on p: the result
 // for a token is bitwise the same in a whole prompt, in a portion or as a single
 // decoded token, whatever pages hold the keys.
+//
+// Two optional rules on top: a cap c on the scores, s <- c tanh(s / c) after the scale; and a sink per query head, a
+// learned number whose exponential joins the softmax's denominator (it has no key and no value and is not scaled): it
+// enters the running maximum and sum after the last group of keys, so the order of the sums stays a function of p.
 #include "common.cuh"
 
 namespace stride {
@@ -55,7 +59,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, const T* __restrict__ k_pages,
                                const T* __restrict__ v_pages, const int32_t* __restrict__ block_table, int table_width,
                                const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions, int nq,
-                               int nkv, int hd, int page_size, float scale, int window) {
+                               int nkv, int hd, int page_size, float scale, int window, float softcap,
+                               const float* __restrict__ sinks) {
     pdl_trigger();
     pdl_wait();
     __shared__ __align__(16) float q_smem[kWarps][kMaxHeadDim];
@@ -92,6 +97,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
             const int page = table[key / page_size];
             const T* k_row = k_pages + ((static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size) * hd;
             s = dot_row<T>(qs, k_row, hd) * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = ok ? expf(s - m_new) : 0.f;
@@ -115,6 +121,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
         }
         m = m_new;
     }
+    if (sinks) {
+        const float sink = sinks[head];
+        const float m_new = fmaxf(m, sink);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sink - m_new);
+#pragma unroll
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= corr;
+    }
     const float inv = 1.f / l;
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) {
@@ -132,8 +146,9 @@ using namespace stride;
 extern "C" int stride_paged_attention_generic(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                               const int32_t* block_table, int table_width, const int32_t* seq_of_token,
                                               const int32_t* positions, int tokens, int nq, int nkv, int hd, int page_size,
-                                              float scale, int window, int dtype, cudaStream_t stream) {
-    if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || table_width <= 0 || window < 0) return STRIDE_BAD_ARGUMENT;
+                                              float scale, int window, float softcap, const float* sinks, int dtype,
+                                              cudaStream_t stream) {
+    if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || softcap < 0.f) return STRIDE_BAD_ARGUMENT;
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
     if (hd % 16 || hd > kMaxHeadDim) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
@@ -141,12 +156,12 @@ extern "C" int stride_paged_attention_generic(const void* q, int q_stride, void*
     if (dtype == STRIDE_DTYPE_F32)
         stride::launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(kWarps * 32), 0, stream, 
             static_cast<const float*>(q), q_stride, static_cast<float*>(out), static_cast<const float*>(k_pages),
-            static_cast<const float*>(v_pages), block_table, table_width, seq_of_token, positions, nq, nkv, hd, page_size, scale, window);
+            static_cast<const float*>(v_pages), block_table, table_width, seq_of_token, positions, nq, nkv, hd, page_size, scale, window, softcap, sinks);
     else if (dtype == STRIDE_DTYPE_BF16)
         stride::launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(kWarps * 32), 0, stream, 
             static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<__nv_bfloat16*>(out),
             static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages), block_table, table_width,
-            seq_of_token, positions, nq, nkv, hd, page_size, scale, window);
+            seq_of_token, positions, nq, nkv, hd, page_size, scale, window, softcap, sinks);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

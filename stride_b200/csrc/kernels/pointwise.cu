@@ -1,0 +1,167 @@
+// Small elementwise kernels that several mixers, feed-forwards and heads share. All arithmetic is float32; storage is
+// float32 or bfloat16. One 16-byte pack per thread where pointers and sizes allow it (the form that streams fastest
+// here), one element per thread otherwise.
+//
+//   gated_act     out = act(gate) * up for [tokens, 2 * inter] whose gate and up columns alternate in blocks
+//                 (the layout of the fused gate/up product); act: 0 SiLU, 1 the tanh form of GELU
+//   sigmoid_gate  x *= sigmoid(g)
+//   softcap       x = c tanh(x / c)            (float32, in place: logits)
+//   tanh_inplace  x = tanh(x)
+#include "common.cuh"
+
+namespace stride {
+
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+    static constexpr int V = 4;
+    float v[4];
+    __device__ __forceinline__ void load(const float* p) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+    static constexpr int V = 8;
+    float v[8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+        uint4 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+
+__device__ __forceinline__ float act_f(float g, int act) {
+    if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.f + expf(-g));
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+template <typename T>
+__global__ void gated_act_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, int act, size_t packs) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int V = Vec<T>::V;
+    const int per_row = inter / V;
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= packs) return;
+    const size_t t = idx / per_row;
+    const int i = static_cast<int>(idx - t * per_row) * V;
+    const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
+    Vec<T> g, u;
+    g.load(in + at);
+    u.load(in + at + block);
+#pragma unroll
+    for (int j = 0; j < V; ++j) g.v[j] = act_f(g.v[j], act) * u.v[j];
+    g.store(out + t * inter + i);
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, int act, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / inter;
+    const int i = static_cast<int>(idx - t * inter);
+    const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
+    out[idx] = from_f32<T>(act_f(to_f32(in[at]), act) * to_f32(in[at + block]));
+}
+
+// op: 0  x *= sigmoid(g);  1  x = cap * tanh(x / cap);  2  x = tanh(x)
+template <typename T>
+__global__ void unary_vec_kernel(T* __restrict__ x, const T* __restrict__ g, int op, float cap, size_t packs) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int V = Vec<T>::V;
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= packs) return;
+    Vec<T> a, b;
+    a.load(x + idx * V);
+    if (op == 0) b.load(g + idx * V);
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+        a.v[j] = op == 0 ? a.v[j] * sigmoid_f(b.v[j]) : op == 1 ? cap * tanhf(a.v[j] / cap) : tanhf(a.v[j]);
+    a.store(x + idx * V);
+}
+
+template <typename T>
+__global__ void unary_kernel(T* __restrict__ x, const T* __restrict__ g, int op, float cap, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    const float a = to_f32(x[idx]);
+    x[idx] = from_f32<T>(op == 0 ? a * sigmoid_f(to_f32(g[idx])) : op == 1 ? cap * tanhf(a / cap) : tanhf(a));
+}
+
+template <typename T>
+int unary(void* x, const void* g, int op, float cap, long long n, cudaStream_t stream) {
+    constexpr int V = Vec<T>::V;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g);
+    if (bits % 16 == 0 && n % V == 0) {
+        const size_t packs = static_cast<size_t>(n) / V;
+        stride::launch(unary_vec_kernel<T>, dim3(static_cast<unsigned>((packs + 127) / 128)), dim3(128), 0, stream, static_cast<T*>(x),
+                       static_cast<const T*>(g), op, cap, packs);
+    } else {
+        stride::launch(unary_kernel<T>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream, static_cast<T*>(x),
+                       static_cast<const T*>(g), op, cap, static_cast<size_t>(n));
+    }
+    return STRIDE_LAUNCH_STATUS();
+}
+
+template <typename T>
+int gated(const void* in, void* out, int tokens, int inter, int block, int act, cudaStream_t stream) {
+    constexpr int V = Vec<T>::V;
+    const size_t total = static_cast<size_t>(tokens) * inter;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out);
+    if (bits % 16 == 0 && block % V == 0) {
+        const size_t packs = total / V;
+        stride::launch(gated_act_vec_kernel<T>, dim3(static_cast<unsigned>((packs + 127) / 128)), dim3(128), 0, stream,
+                       static_cast<const T*>(in), static_cast<T*>(out), inter, block, act, packs);
+    } else {
+        stride::launch(gated_act_kernel<T>, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, static_cast<const T*>(in),
+                       static_cast<T*>(out), inter, block, act, total);
+    }
+    return STRIDE_LAUNCH_STATUS();
+}
+
+}  // namespace stride
+
+using namespace stride;
+
+extern "C" {
+
+int stride_gated_act(const void* in, void* out, int tokens, int inter, int block, int act, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || inter <= 0 || block <= 0 || inter % block || act < 0 || act > 1) return STRIDE_BAD_ARGUMENT;
+    if (static_cast<size_t>(tokens) * inter / 4 / 128 > 0x7fffffffull) return STRIDE_UNSUPPORTED;
+    if (tokens == 0) return 0;
+    if (dtype == STRIDE_DTYPE_F32) return gated<float>(in, out, tokens, inter, block, act, stream);
+    if (dtype == STRIDE_DTYPE_BF16) return gated<__nv_bfloat16>(in, out, tokens, inter, block, act, stream);
+    return STRIDE_BAD_ARGUMENT;
+}
+
+int stride_pointwise(void* x, const void* g, int op, float cap, long long n, int dtype, cudaStream_t stream) {
+    if (n < 0 || op < 0 || op > 2 || (op == 0 && g == nullptr) || (op == 1 && !(cap > 0.f))) return STRIDE_BAD_ARGUMENT;
+    if (n / 4 / 128 > 0x7fffffffll) return STRIDE_UNSUPPORTED;
+    if (n == 0) return 0;
+    if (dtype == STRIDE_DTYPE_F32) return unary<float>(x, g, op, cap, n, stream);
+    if (dtype == STRIDE_DTYPE_BF16) return unary<__nv_bfloat16>(x, g, op, cap, n, stream);
+    return STRIDE_BAD_ARGUMENT;
+}
+
+}  // extern "C"

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                                             c_int, c_int, c_void_p]),
+                                                             c_int, c_float, c_void_p, c_int, c_void_p]),
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
     "stride_gemm_tc_clustered": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -110,6 +110,20 @@ _SIGNATURES = {
                                     c_void_p]),
     "stride_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_relu_squared": ("moe", [c_void_p, c_longlong, c_int, c_void_p]),
+    "stride_gated_act": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_pointwise": ("pointwise", [c_void_p, c_void_p, c_int, c_float, c_longlong, c_int, c_void_p]),
+    "stride_delta_prepare": ("linear_recurrence", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
+                                                   c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "stride_delta_scan": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p,
+                                                c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p]),
+    "stride_bonus_scan": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_shift_mix": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_head_norm_gate": ("linear_recurrence", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                                                    c_float, c_int, c_void_p]),
 }
 
 
@@ -141,7 +155,10 @@ _CLASS_OF = {
     "stride_moe_select": "router", "stride_rglru_conv": "recurrent block: convolution",
     "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_rglru_scan_pieces": "recurrent block: recurrence", "stride_moe_route": "router",
     "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
-    "stride_relu_squared": "relu^2",
+    "stride_relu_squared": "relu^2", "stride_gated_act": "act * up", "stride_pointwise": "gates and caps",
+    "stride_delta_prepare": "delta rule: convolution, unit vectors, decay", "stride_delta_scan": "delta rule: recurrence",
+    "stride_bonus_scan": "decayed memory: recurrence", "stride_shift_mix": "decayed memory: token shift",
+    "stride_head_norm_gate": "per-head norm and gate",
 }
 
 
@@ -303,6 +320,102 @@ def silu_mul(inp, out, block: int | None = None) -> None:
         raise KernelError("silu_mul wants [tokens, 2*inter] in and [tokens, inter] out of one element type")
     _check(_fn("stride_silu_mul")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, inter if block is None else int(block),
                                   _code(out.dtype), _stream()), "silu_mul")
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(inp, out, block: int | None = None, activation: str = "silu") -> None:
+    """``silu_mul`` for any activation of ``ACTIVATIONS``: ``out = act(gate) * up``, same layout of ``inp``."""
+    tokens, inter = out.shape
+    if inp.shape != (tokens, 2 * inter) or inp.dtype != out.dtype:
+        raise KernelError("gated_act wants [tokens, 2*inter] in and [tokens, inter] out of one element type")
+    _check(_fn("stride_gated_act")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, inter if block is None else int(block),
+                                   ACTIVATIONS[activation], _code(out.dtype), _stream()), "gated_act")
+
+
+def sigmoid_gate(x, gate) -> None:
+    """``x *= sigmoid(gate)`` elementwise, in float32 arithmetic."""
+    if gate.shape != x.shape or gate.dtype != x.dtype:
+        raise KernelError("sigmoid_gate: x and gate must agree in shape and element type")
+    _check(_fn("stride_pointwise")(_dev(x, "x"), _dev(gate, "gate"), 0, 0.0, x.numel(), _code(x.dtype), _stream()), "sigmoid_gate")
+
+
+def softcap_(x, cap: float) -> None:
+    """``x = cap * tanh(x / cap)`` in place."""
+    _check(_fn("stride_pointwise")(_dev(x, "x"), None, 1, float(cap), x.numel(), _code(x.dtype), _stream()), "softcap")
+
+
+def tanh_(x) -> None:
+    _check(_fn("stride_pointwise")(_dev(x, "x"), None, 2, 0.0, x.numel(), _code(x.dtype), _stream()), "tanh")
+
+
+# ------------------------------------------------------------ matrix memories (delta rule, decayed memory with a bonus)
+def delta_prepare(proj, conv_w, low, a_log, dt_bias, state, tail_off: int, seq_of_token, q_start, state_slot, qk, v, beta, decay,
+                  G: int, H: int, D: int, DV: int, taps: int, unit_eps: float) -> None:
+    """Per token of the step, from ``proj`` [tokens, >= 2GD + HV + H] (q, k, v, beta's projection) and ``low`` (float32,
+    its first HD columns the decay's projection): convolution with SiLU, unit-length q and k, beta, and decay - 1, all
+    float32. ``state`` [slots, n] float32 holds the convolution's tail [taps - 1, 2GD + HV] at ``tail_off``."""
+    tokens = proj.shape[0]
+    C = 2 * G * D + H * DV
+    if proj.shape[1] < C + H or conv_w.shape != (C, taps) or low.shape[1] < H * D:
+        raise KernelError("delta_prepare: shapes do not agree")
+    _check(_fn("stride_delta_prepare")(
+        _dev(proj, "proj"), proj.shape[1], _dev(conv_w, "conv_w", torch.float32), _dev(low, "low", torch.float32), low.shape[1],
+        _dev(a_log, "a_log", torch.float32), _dev(dt_bias, "dt_bias", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
+        int(tail_off), _dev(seq_of_token, "seq_of_token", torch.int32), _dev(q_start, "q_start", torch.int32),
+        _dev(state_slot, "state_slot", torch.int32), _dev(qk, "qk", torch.float32), _dev(v, "v", torch.float32),
+        _dev(beta, "beta", torch.float32), _dev(decay, "decay", torch.float32), tokens, G, H, D, DV, taps, float(unit_eps),
+        _code(proj.dtype), _stream()), "delta_prepare")
+
+
+def delta_scan(qk, v, beta, decay, o, state, tail_off: int, proj, q_start, q_len, state_slot, num_seqs: int, G: int, H: int, D: int,
+               DV: int, taps: int) -> None:
+    """The gated delta rule over every request of the step, in token order: ``o`` [tokens, H * DV] float32; S and the
+    convolution's tail in ``state`` move on."""
+    _check(_fn("stride_delta_scan")(
+        _dev(qk, "qk", torch.float32), _dev(v, "v", torch.float32), _dev(beta, "beta", torch.float32), _dev(decay, "decay", torch.float32),
+        _dev(o, "o", torch.float32), _dev(state, "state", torch.float32), state.shape[1], int(tail_off), _dev(proj, "proj"), proj.shape[1],
+        _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32), num_seqs,
+        G, H, D, DV, taps, _code(proj.dtype), _stream()), "delta_scan")
+
+
+def bonus_scan(r, k, v, wlog, w0, bonus, o, state, q_start, q_len, state_slot, num_seqs: int, H: int, D: int) -> None:
+    """Decayed memory with a bonus for the current token: ``o_t = (S + diag(bonus) k v^T)^T r``, then
+    ``S = diag(exp(-exp(wlog + w0))) S + k v^T``; r, k, v [tokens, H * D] in one element type, the rest float32."""
+    if not (r.dtype == k.dtype == v.dtype):
+        raise KernelError("bonus_scan: r, k and v must have one element type")
+    _check(_fn("stride_bonus_scan")(
+        _dev(r, "r"), _dev(k, "k"), _dev(v, "v"), _dev(wlog, "wlog", torch.float32), _dev(w0, "w0", torch.float32),
+        _dev(bonus, "bonus", torch.float32), _dev(o, "o", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
+        _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32), num_seqs,
+        H, D, _code(r.dtype), _stream()), "bonus_scan")
+
+
+def shift_mix(x, mu, state, prev_off: int, seq_of_token, q_start, q_len, state_slot, out) -> None:
+    """``out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s]`` with the request's last input before the step (``state`` at
+    ``prev_off``) in front of its first token; the step's last input is stored there afterwards."""
+    tokens, width = x.shape
+    mixes = mu.shape[0]
+    if out.shape != (mixes, tokens, width) or out.dtype != x.dtype or mu.shape[1] != width:
+        raise KernelError("shift_mix: shapes do not agree")
+    _check(_fn("stride_shift_mix")(
+        _dev(x, "x"), _dev(mu, "mu", torch.float32), _dev(state, "state", torch.float32), state.shape[1], int(prev_off),
+        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
+        _dev(state_slot, "state_slot", torch.int32), _dev(out, "out"), tokens, width, mixes, _code(x.dtype), _stream()), "shift_mix")
+
+
+def head_norm_gate(o, weight, per_head_weight: bool, gate, gate_kind: str, out, H: int, DV: int, eps: float, gate_off: int = 0) -> None:
+    """``out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * gate`` per head. ``weight`` [DV] for all heads or
+    [H * DV]; ``gate`` [tokens, >= gate_off + H * DV], read from column ``gate_off`` on: ``sigmoid`` of float32 values or
+    ``silu`` of values in ``out``'s type."""
+    tokens = o.shape[0]
+    kind = {"sigmoid": 0, "silu": 1}[gate_kind]
+    _check(_fn("stride_head_norm_gate")(
+        _dev(o, "o", torch.float32), _dev(weight, "weight", torch.float32), DV if per_head_weight else 0,
+        _dev(gate, "gate", torch.float32 if kind == 0 else out.dtype) + gate_off * gate.element_size(), gate.shape[1], kind,
+        _dev(out, "out"), tokens, H, DV, float(eps),
+        _code(out.dtype), _stream()), "head_norm_gate")
 
 
 # ------------------------------------------------------------ Dynamic Tanh, scaled sums
@@ -935,21 +1048,24 @@ def linear(x, weight, out) -> None:
 
 # -------------------------------------------------------------------- attention
 def paged_attention(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, nq: int, nkv: int,
-                    hd: int, page_size: int, scale: float, window: int = 0) -> None:
+                    hd: int, page_size: int, scale: float, window: int = 0, softcap: float = 0.0, sinks=None) -> None:
     """Attention of every token in the flat batch over its request's pages.
-    ``q`` holds head h of token t at ``q[t * q_stride + h * hd]``."""
+    ``q`` holds head h of token t at ``q[t * q_stride + h * hd]``. ``softcap`` c > 0 caps the scaled scores at
+    c tanh(s / c); ``sinks`` (float32 [nq]) adds exp(sink) of the head to the softmax's denominator."""
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
     _check(_fn("stride_paged_attention_generic")(
         _dev(q, "q"), q_stride, _dev(out, "out"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
-        _dev(positions, "positions", torch.int32), tokens, nq, nkv, hd, page_size, float(scale), int(window),
-        _code(q.dtype), _stream()), "paged_attention")
+        _dev(positions, "positions", torch.int32), tokens, nq, nkv, hd, page_size, float(scale), int(window), float(softcap),
+        _opt(sinks, "sinks", torch.float32), _code(q.dtype), _stream()), "paged_attention")
 
 
-def fast_attention_supported(dtype, nq: int, nkv: int, hd: int) -> bool:
-    """Sizes that the tensor-core attention kernels run; others use the generic kernel."""
+def fast_attention_supported(dtype, nq: int, nkv: int, hd: int, softcap: float = 0.0, sinks: bool = False) -> bool:
+    """Sizes and rules that the tensor-core attention kernels run; others use the generic kernel."""
+    if softcap or sinks:
+        return False
     return dtype == torch.bfloat16 and hd in (64, 128) and nq % nkv == 0 and nq // nkv <= 16
 
 

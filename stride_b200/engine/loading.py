@@ -32,7 +32,8 @@ def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda", token_cap
     """``min_positions``: position tables for at least this many positions, where the configuration can give them
     (``with_max_positions``), even if the checkpoint names a shorter length."""
     source = SafetensorsSource(model_dir)
-    config = load_config(model_dir, tensor_names=source.names())
+    names = source.names()
+    config = load_config(model_dir, tensor_names=names, tensor_shapes={n: tuple(source.describe(n)[0]) for n in names})
     spec_positions = getattr(config, "max_position_embeddings", None)
     if min_positions and spec_positions is not None and spec_positions < min_positions and hasattr(config, "with_max_positions"):
         config = config.with_max_positions(min_positions)

@@ -1,5 +1,5 @@
-from . import (attention, block, dyt, ends, latent_attention, rglru, rmsnorm, rope, routed_experts, swiglu,  # noqa: F401
-               token_side)  # (registers the built-in kinds)
+from . import (attention, block, dyt, ends, latent_attention, matrix_memory, parallel, rglru, rmsnorm, rope, routed_experts,  # noqa: F401
+               swiglu, token_side)  # (registers the built-in kinds)
 from .base import (CATEGORIES, CacheRequest, Embedding, FeedForward, Head, Layer, Mixer, Norm, Part, PositionEncoding, StateRequest,
                    StreamInput, TensorDecl, build_part, register_part, registered_parts)
 from .model import DecoderModel

@@ -5,6 +5,23 @@ encoding and cache write, attention of every token over its request's pages,
 output projection: python/stride_worker/model.py:258-299 with the attention rule
 of python/stride_worker/layers.py:109-149. Biases are used when the spec says so.
 A window (not used by Llama 3) limits each token to its last W keys.
+
+Spec params, all optional:
+
+* ``values`` ``keys``: there is no value projection; a token's value is its key as projected (bias included),
+  before the rotation. The key rows are used twice in the fused projection, so keys and values go through the same
+  kernels and pages as ever.
+* ``softcap`` c: scaled scores become c tanh(s / c).
+* ``sinks``: a tensor ``sink`` [heads]; exp(sink_h) joins the denominator of head h's softmax.
+* ``output_gate``: a matrix ``g`` [heads * head_dim, hidden]; the concatenated heads are multiplied by
+  sigmoid(g x) before the output projection.
+* ``names`` ``short``: tensors are ``q, k, v, o`` with biases ``q.b, k.b, v.b`` under the prefix (default:
+  ``q_proj.weight`` and so on).
+
+When the position part asks for another order of a head's entries (``head_permutation``), the rows of the query and
+key projections (and of whatever else must follow them: values taken from keys, the gate, the columns of the output
+projection) are laid out in that order at load; scores and outputs are the same, and ``named_tensors`` gives the
+stored order back.
 """
 
 from __future__ import annotations
@@ -33,39 +50,86 @@ class PagedAttention(Mixer):
         self.scale = float(s.scale)
         self.window = 0 if s.window is None else int(s.window)
         self.position = build_part("position", s.position, runtime)
-        self.w_qkv = self.w_o = self.bias = None
-        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd)
+        p = dict(s.params)
+        self.values_are_keys = p.get("values") == "keys"
+        self.softcap = float(p.get("softcap", 0.0))
+        self.has_sinks, self.gated = bool(p.get("sinks", False)), bool(p.get("output_gate", False))
+        self.short_names = p.get("names") == "short"
+        permutation = getattr(self.position, "head_permutation", lambda: None)()
+        self.perm = None if permutation is None else torch.tensor(permutation, dtype=torch.long)
+        self.w_qkv = self.w_o = self.bias = self.w_gate = self.sinks = None
+        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd, self.softcap, self.has_sinks)
+        self.accepts_folded = not self.gated          # the gate reads the normed input as a tensor
 
     # ----------------------------------------------------------------- weights
     def _names(self):
         p = self.spec.prefix
-        return {k: f"{p}{k}_proj.weight" for k in "qkvo"}, {k: f"{p}{k}_proj.bias" for k in "qkv"}
+        if self.short_names:
+            w, b = {k: p + k for k in "qkvo"}, {k: f"{p}{k}.b" for k in "qkv"}
+        else:
+            w, b = {k: f"{p}{k}_proj.weight" for k in "qkvo"}, {k: f"{p}{k}_proj.bias" for k in "qkv"}
+        w["g"], w["sink"] = p + "g", p + "sink"
+        return w, b
 
     def declare(self):
         w, b = self._names()
         d = {w["q"]: TensorDecl((self.q_dim, self.hidden)), w["k"]: TensorDecl((self.kv_dim, self.hidden)),
-             w["v"]: TensorDecl((self.kv_dim, self.hidden)), w["o"]: TensorDecl((self.hidden, self.q_dim))}
+             w["o"]: TensorDecl((self.hidden, self.q_dim))}
+        if not self.values_are_keys:
+            d[w["v"]] = TensorDecl((self.kv_dim, self.hidden))
         if self.spec.bias:
             d[b["q"]] = TensorDecl((self.q_dim,), "vector")
             d[b["k"]] = TensorDecl((self.kv_dim,), "vector")
-            d[b["v"]] = TensorDecl((self.kv_dim,), "vector")
+            if not self.values_are_keys:
+                d[b["v"]] = TensorDecl((self.kv_dim,), "vector")
+        if self.gated:
+            d[w["g"]] = TensorDecl((self.q_dim, self.hidden))
+        if self.has_sinks:
+            d[w["sink"]] = TensorDecl((self.nq,), "vector")
         d.update(self.position.declare())          # a position encoding may have tensors of its own
         return d
 
+    def _reorder(self, t, inverse: bool = False, dim: int = 0):
+        """The heads' entries of ``t`` along ``dim`` (length heads * head_dim) in the position part's order."""
+        if self.perm is None:
+            return t
+        perm = torch.argsort(self.perm) if inverse else self.perm
+        heads = t.shape[dim] // self.hd
+        index = (torch.arange(heads)[:, None] * self.hd + perm[None, :]).reshape(-1).to(t.device)
+        return t.index_select(dim, index).contiguous()
+
     def bind(self, weights):
         w, b = self._names()
-        self.w_qkv = torch.cat([weights[w["q"]], weights[w["k"]], weights[w["v"]]], dim=0).contiguous()
-        self.w_o = weights[w["o"]]
+        q, k = self._reorder(weights[w["q"]]), self._reorder(weights[w["k"]])
+        v = k if self.values_are_keys else weights[w["v"]]
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        # values taken from keys come in the keys' order, and so do the heads' outputs
+        self.w_o = self._reorder(weights[w["o"]], dim=1) if self.values_are_keys else weights[w["o"]]
         if self.spec.bias:
-            self.bias = torch.cat([weights[b["q"]], weights[b["k"]], weights[b["v"]]]).contiguous()
+            bq, bk = self._reorder(weights[b["q"]]), self._reorder(weights[b["k"]])
+            self.bias = torch.cat([bq, bk, bk if self.values_are_keys else weights[b["v"]]]).contiguous()
+        if self.gated:
+            self.w_gate = self._reorder(weights[w["g"]]) if self.values_are_keys else weights[w["g"]]
+        if self.has_sinks:
+            self.sinks = weights[w["sink"]]
         self.position.bind(weights)
 
     def named_tensors(self):
         w, b = self._names()
         q, k = self.q_dim, self.q_dim + self.kv_dim
-        out = {w["q"]: self.w_qkv[:q], w["k"]: self.w_qkv[q:k], w["v"]: self.w_qkv[k:], w["o"]: self.w_o}
+        back = lambda t, dim=0: self._reorder(t, inverse=True, dim=dim)
+        out = {w["q"]: back(self.w_qkv[:q]), w["k"]: back(self.w_qkv[q:k]),
+               w["o"]: back(self.w_o, 1) if self.values_are_keys else self.w_o}
+        if not self.values_are_keys:
+            out[w["v"]] = self.w_qkv[k:]
         if self.bias is not None:
-            out.update({b["q"]: self.bias[:q], b["k"]: self.bias[q:k], b["v"]: self.bias[k:]})
+            out.update({b["q"]: back(self.bias[:q]), b["k"]: back(self.bias[q:k])})
+            if not self.values_are_keys:
+                out[b["v"]] = self.bias[k:]
+        if self.gated:
+            out[w["g"]] = back(self.w_gate) if self.values_are_keys else self.w_gate
+        if self.has_sinks:
+            out[w["sink"]] = self.sinks
         out.update(self.position.named_tensors())
         return out
 
@@ -75,7 +139,7 @@ class PagedAttention(Mixer):
 
     # ----------------------------------------------------------------- forward
     lazy_output = True
-    accepts_folded = True
+    accepts_folded = True       # an instance with an output gate says False
 
     def forward(self, x, ctx, cache, lazy_output: bool = False):
         tokens = x.shape[0]
@@ -88,6 +152,10 @@ class PagedAttention(Mixer):
             self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
         attn = self.rt.buffer("attn", tokens, self.q_dim)
         self._attend(qkv, attn, ctx, cache, tokens)
+        if self.gated:
+            gate = self.rt.buffer("attn_gate", tokens, self.q_dim)
+            ops.linear(x, self.w_gate, gate)
+            ops.sigmoid_gate(attn, gate)
         if lazy_output:
             return Projection(attn, self.w_o)          # the residual stream runs it, with the sum and norm that follow if it can
         out = self.rt.buffer("mixer_out", tokens, self.hidden)
@@ -118,7 +186,7 @@ class PagedAttention(Mixer):
         if not self._fast:
             # the exact kernel: the whole 32-bit path, and bfloat16 sizes the tensor-core kernels refuse
             ops.paged_attention(qkv, self.qkv_dim, attn, cache.k_pages, cache.v_pages, table, ctx.seq_of_token[:tokens],
-                                ctx.positions[:tokens], *geometry)
+                                ctx.positions[:tokens], *geometry, self.softcap, self.sinks)
             return
         split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
         if split > 0:

@@ -4,7 +4,8 @@
 (python/stride_worker/model.py:250-252). ``linear``: logits are the normed rows times the head matrix, computed in
 the compute dtype and returned in float32; a head whose spec names no tensor shares the embedding table
 (python/stride_worker/model.py:127-130, 322-341). An architecture that scales its embedding, adds a bias to its
-head or caps its logits registers another kind; the model itself does not change.
+head registers another kind; the model itself does not change. A ``linear`` head whose spec gives the param
+``softcap`` c caps its logits at c tanh(logits / c).
 """
 
 from __future__ import annotations
@@ -56,6 +57,9 @@ class LinearHead(Head):
 
     def forward(self, x, out):
         ops.linear(x, self.weight, out)
+        cap = dict(self.spec.params).get("softcap")
+        if cap:         # logits <- cap * tanh(logits / cap), in float32
+            ops.softcap_(out, float(cap))
 
 
 register_part("embedding", "lookup", LookupEmbedding)

@@ -1,5 +1,8 @@
 """RMSNorm: ``x * rsqrt(mean(x^2) + eps) * weight`` in float32, the weight
-multiplying after the normalisation (python/stride_worker/layers.py:24-35)."""
+multiplying after the normalisation (python/stride_worker/layers.py:24-35).
+
+Spec params: ``tensor`` names the weight (default: the prefix + ``weight``); ``weight_offset`` c makes the factor
+``c + w`` for checkpoints that keep w = factor - c (the sum is formed once, in float32, when the weight is bound)."""
 
 from __future__ import annotations
 
@@ -13,16 +16,20 @@ class RMSNorm(Norm):
         self.eps = float(spec.eps)
         self.width = int(spec.width)
         self.weight = None
-        self._name = spec.prefix + "weight"
+        p = dict(spec.params)
+        self._name = p.get("tensor", spec.prefix + "weight")
+        self.offset = float(p.get("weight_offset", 0.0))
+        self.stored = None
 
     def declare(self):
         return {self._name: TensorDecl((self.width,), "vector")}
 
     def bind(self, weights):
-        self.weight = weights[self._name]
+        self.stored = weights[self._name]
+        self.weight = self.stored + self.offset if self.offset else self.stored
 
     def named_tensors(self):
-        return {self._name: self.weight}
+        return {self._name: self.stored}
 
     def fold_inputs(self):
         return self.weight, self.eps

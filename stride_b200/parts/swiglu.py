@@ -1,4 +1,4 @@
-"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))``
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, act SiLU or the tanh form of GELU
 (python/stride_worker/layers.py:152-161). Gate and up are one matrix product
 (their weights are stacked at load time); SiLU and the product run in float32.
 
@@ -25,13 +25,17 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torc
 class SwiGLU(FeedForward):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not supported by the swiglu kernel (silu only)")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not supported by the gated feed-forward (one of {sorted(ops.ACTIVATIONS)} is)")
+        self.activation = spec.activation
+        self.short_names = dict(spec.params).get("names") == "short"
         self.hidden, self.inter = spec.hidden, spec.intermediate
         self.w_gate_up = self.w_down = None
 
     def _names(self):
         p = self.spec.prefix
+        if self.short_names:
+            return p + "gate", p + "up", p + "down"
         return p + "gate_proj.weight", p + "up_proj.weight", p + "down_proj.weight"
 
     def declare(self):
@@ -58,7 +62,8 @@ class SwiGLU(FeedForward):
         tokens = x.shape[0]
         act = self.rt.buffer("ffn_act", tokens, self.inter)
         folded = x if isinstance(x, ops.FoldedNorm) else None
-        gated = self.block == ops.GATED_BLOCK and (
+        # the products that apply the activation in their epilogue know SiLU only
+        gated = self.activation == "silu" and self.block == ops.GATED_BLOCK and (
             ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded)
             or (ops.rows_wanted(tokens) and ops.linear_rows_gated(folded.xt if folded else x, self.w_gate_up, act, folded)))
         if not gated:
@@ -66,7 +71,10 @@ class SwiGLU(FeedForward):
                 x = folded.tensor()
             gate_up = self.rt.buffer("gate_up", tokens, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gate_up)
-            ops.silu_mul(gate_up, act, self.block)
+            if self.activation == "silu":
+                ops.silu_mul(gate_up, act, self.block)
+            else:
+                ops.gated_act(gate_up, act, self.block, self.activation)
         if lazy_output:
             return Projection(act, self.w_down)        # the residual stream runs it, with the sum and norm that follow if it can
         out = self.rt.buffer("ffn_out", tokens, self.hidden)
