@@ -1,5 +1,5 @@
 // Paged attention for any mix of prompt portions and decoded tokens, in float32
-// or bfloat16 storage with float32 arithmetic. This is the exact, slower kernel:
+// or bfloat16 storage with float32 arithmetic, any head size up to 256. This is the exact, slower kernel:
 // the whole 32-bit path runs on it, and the bfloat16 path falls back to it for
 // head sizes or windows that the tensor-core kernels refuse.
 //
@@ -28,6 +28,10 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* _
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
     float acc = 0.f;
+    if (hd & 3) {       // rows that do not start on 16-byte boundaries: one entry at a time
+        for (int d = 0; d < hd; ++d) acc = fmaf(q[d], k[d], acc);
+        return acc;
+    }
     for (int d = 0; d < hd; d += 4) {
         const float4 kv = *reinterpret_cast<const float4*>(k + d);
         acc = fmaf(q[d], kv.x, acc);
@@ -41,6 +45,10 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, con
 template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int hd) {
     float acc = 0.f;
+    if (hd & 7) {
+        for (int d = 0; d < hd; ++d) acc = fmaf(q[d], __bfloat162float(k[d]), acc);
+        return acc;
+    }
     for (int d = 0; d < hd; d += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
         const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -150,7 +158,7 @@ extern "C" int stride_paged_attention_generic(const void* q, int q_stride, void*
                                               cudaStream_t stream) {
     if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || softcap < 0.f) return STRIDE_BAD_ARGUMENT;
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
-    if (hd % 16 || hd > kMaxHeadDim) return STRIDE_UNSUPPORTED;
+    if (hd > kMaxHeadDim) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
     dim3 grid(tokens, (nq + kWarps - 1) / kWarps);
     if (dtype == STRIDE_DTYPE_F32)

@@ -25,7 +25,7 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
                      const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                      const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                      const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
-                     int page_size, float scale_log2e, int window) {
+                     int page_size, float scale_log2e, int window, float cap_in, const float* __restrict__ sinks) {
     pdl_trigger();
     pdl_wait();
     constexpr int ROW_BYTES = HD * 2;
@@ -140,6 +140,12 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
                 mma_bf16_16816(s[2 * kb + 1], qa[kk], b[2], b[3]);
             }
         }
+        if (cap_in > 0.f) {     // capped scores: c tanh(scale s / c); scale_log2e then holds c log2(e)
+#pragma unroll
+            for (int nt = 0; nt < kKTile / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = tanh_approx(s[nt][e] * cap_in);
+        }
         float mx[2] = {-INFINITY, -INFINITY};
         // Only tiles that touch the diagonal or the window's edge need the mask.
         const int warp_first_pos = pos0 + min(wr0, rows - 1);
@@ -212,6 +218,8 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        // a sink joins the denominator: exp(sink - m), with m in log2 units
+        if (sinks && m[r] != -INFINITY) l[r] += exp2f(fmaf(sinks[head], 1.4426950408889634f, -m[r]));
     }
     __nv_bfloat16* out_base = out + static_cast<size_t>(q_start[seq] + row0) * nq * HD + static_cast<size_t>(head) * HD;
 #pragma unroll
@@ -230,7 +238,7 @@ template <int HD>
 int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, const __nv_bfloat16* k_pages,
                    const __nv_bfloat16* v_pages, const int32_t* block_table, int table_width, const int32_t* q_start,
                    const int32_t* q_len, const int32_t* ctx_len, int num_seqs, int max_tiles, int nq, int nkv, int page_size,
-                   float scale, int window, cudaStream_t stream) {
+                   float scale, int window, float softcap, const float* sinks, cudaStream_t stream) {
     const int smem = 2 * 2 * kKTile * HD * 2;
     static bool configured = false;
     if (!configured) {
@@ -241,7 +249,8 @@ int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, con
     dim3 grid(max_tiles, nq);
     stride::launch(paged_prefill_kernel<HD>, dim3(grid), dim3(128), smem, stream, q, q_stride, out, k_pages, v_pages, block_table, table_width, q_start,
                                                           q_len, ctx_len, num_seqs, nq, nkv, page_size,
-                                                          scale * 1.4426950408889634f, window);
+                                                          (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window,
+                                                          softcap > 0.f ? scale / softcap : 0.f, sinks);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -252,12 +261,15 @@ using namespace stride;
 // Attention for the first `num_seqs` requests of the step, which own the first
 // `tokens` rows of the flat batch. q: [tokens, q_stride]; out: [tokens, nq * hd].
 // Returns -2 for sizes it does not run (head sizes other than 64 and 128); the
-// caller then uses the generic kernel.
+// caller then uses the generic kernel. softcap c > 0 caps the scaled scores at c tanh(s / c) (with the hardware's tanh);
+// sinks (float32 [nq] or null) adds exp(sink) of the head to the softmax's denominator.
 extern "C" int stride_paged_prefill_attention(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                               const int32_t* block_table, int table_width, const int32_t* q_start,
                                               const int32_t* q_len, const int32_t* ctx_len, int num_seqs, int tokens, int nq,
-                                              int nkv, int hd, int page_size, float scale, int window, cudaStream_t stream) {
-    if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0) return STRIDE_BAD_ARGUMENT;
+                                              int nkv, int hd, int page_size, float scale, int window, float softcap,
+                                              const float* sinks, cudaStream_t stream) {
+    if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || softcap < 0.f)
+        return STRIDE_BAD_ARGUMENT;
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
     if ((hd != 64 && hd != 128) || nq > 65535 || q_stride % 2) return STRIDE_UNSUPPORTED;
     if (tokens == 0 || num_seqs == 0) return 0;
@@ -268,7 +280,7 @@ extern "C" int stride_paged_prefill_attention(const void* q, int q_stride, void*
     auto vp = static_cast<const __nv_bfloat16*>(v_pages);
     if (hd == 64)
         return launch_prefill<64>(qp, q_stride, op, kp, vp, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles,
-                                  nq, nkv, page_size, scale, window, stream);
+                                  nq, nkv, page_size, scale, window, softcap, sinks, stream);
     return launch_prefill<128>(qp, q_stride, op, kp, vp, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles,
-                               nq, nkv, page_size, scale, window, stream);
+                               nq, nkv, page_size, scale, window, softcap, sinks, stream);
 }

@@ -66,7 +66,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                        const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                        const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
-                       int page_shift, float scale_log2e, int window, int* __restrict__ status) {
+                       int page_shift, float scale_log2e, int window, float cap_in, const float* __restrict__ sinks,
+                       int* __restrict__ status) {
     constexpr int HALVES = HD / 64;                       // 64-column boxes per row
     constexpr int HALF_BYTES = kQRows * 128;              // a [128 rows x 64 columns] bf16 box of Q
     constexpr int KV_HALF_BYTES = kKeys * 128;            // [64 keys x 64 columns] of K or V
@@ -327,6 +328,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float sv[64];                                    // raw scores; a masked one is -inf
 #pragma unroll
             for (int i = 0; i < 64; ++i) sv[i] = __uint_as_float(sr[i]);
+            if (cap_in > 0.f) {     // capped scores: c tanh(scale s / c); scale_log2e then holds c log2(e)
+#pragma unroll
+                for (int i = 0; i < 64; ++i) sv[i] = tanh_approx(sv[i] * cap_in);
+            }
             if (edge) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
@@ -414,6 +419,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok) ok = output_done(n_tiles - 1, 17);
         tc_fence_after();
         if (ok) {
+            // a sink joins the denominator: exp(sink - m), with m in log2 units
+            if (sinks != nullptr && m_ref != -INFINITY) l += ex2_approx(fmaf(sinks[head], 1.4426950408889634f, -m_ref));
             // tcgen05.ld is a warp-wide instruction: rows past the portion's end take part and store nothing
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + (static_cast<size_t>(q_row0 + row) * nq + head) * HD;
@@ -441,8 +448,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD, int HEADS>
 int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtensorMap* map_v, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, __nv_bfloat16* out,
                 const int32_t* block_table, int table_width, const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
-                int num_seqs, int max_tiles, int nq, int nkv, int page_shift, float scale, int window, int* status,
-                cudaStream_t stream) {
+                int num_seqs, int max_tiles, int nq, int nkv, int page_shift, float scale, int window, float softcap,
+                const float* sinks, int* status, cudaStream_t stream) {
     constexpr int stages = HEADS == 1 ? 2 : 4;
     constexpr int smem = (HD / 64) * (HEADS * kQRows * 128 + 2 * stages * kKeys * 128) + 1024;      // Q tiles, key ring, value ring
     static bool configured[64] = {};        // the shared-memory limit is set per kernel and device
@@ -457,12 +464,12 @@ int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtens
     const dim3 grid(nq / HEADS, max_tiles), block(HEADS == 1 ? 256 : 512);
     if (map_k != nullptr && map_v != nullptr)
         stride::launch(attn_prefill_tc_kernel<HD, HEADS, true>, grid, block, smem, stream, *map_q, *map_k, *map_v, k_pages, v_pages, out,
-                       block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift, scale * 1.4426950408889634f,
-                       window, status);
+                       block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift,
+                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, status);
     else
         stride::launch(attn_prefill_tc_kernel<HD, HEADS, false>, grid, block, smem, stream, *map_q, *map_q, *map_q, k_pages, v_pages, out,
-                       block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift, scale * 1.4426950408889634f,
-                       window, status);
+                       block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift,
+                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, status);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -493,13 +500,15 @@ static bool kv_tma() {
 // the flat batch. q: [tokens, q_stride] bf16 (head h at columns h*hd); out: [tokens, nq*hd];
 // pages: [num_pages, nkv, page_size, hd]. Returns -2 for what it does not take (head sizes other
 // than 64 and 128, page sizes that are no power of two from 4 to 64, unaligned strides); the caller
-// then uses the mma.sync kernel.
+// then uses the mma.sync kernel. softcap c > 0 caps the scaled scores at c tanh(s / c) (with the hardware's tanh); sinks
+// (float32 [nq] or null) adds exp(sink) of the head to the softmax's denominator.
 extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                                  int num_pages, const int32_t* block_table, int table_width,
                                                  const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
                                                  int num_seqs, int tokens, int nq, int nkv, int hd, int page_size, float scale,
-                                                 int window, int* status, cudaStream_t stream) {
-    if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || num_pages <= 0)
+                                                 int window, float softcap, const float* sinks, int* status, cudaStream_t stream) {
+    if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || num_pages <= 0 ||
+        softcap < 0.f)
         return STRIDE_BAD_ARGUMENT;
     if (nq % nkv || status == nullptr) return STRIDE_BAD_ARGUMENT;
     if ((hd != 64 && hd != 128) || page_size > tc::kKeys || page_size < 4 || q_stride % 8 || nq > 65535) return STRIDE_UNSUPPORTED;
@@ -531,7 +540,7 @@ extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, vo
     }
 #define STRIDE_ATTN_LAUNCH(HD_, HEADS_)                                                                                          \
     tc::launch_attn<HD_, HEADS_>(map_q, map_k, map_v, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq, \
-                                 nkv, page_shift, scale, window, status, stream)
+                                 nkv, page_shift, scale, window, softcap, sinks, status, stream)
     if (hd == 64) return pair ? STRIDE_ATTN_LAUNCH(64, 2) : STRIDE_ATTN_LAUNCH(64, 1);
     return pair ? STRIDE_ATTN_LAUNCH(128, 2) : STRIDE_ATTN_LAUNCH(128, 1);
 #undef STRIDE_ATTN_LAUNCH

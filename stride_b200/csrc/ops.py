@@ -67,12 +67,15 @@ _SIGNATURES = {
     "stride_paged_decode_attention_tma": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                                c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                                                                c_int, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "stride_paged_decode_attention_rules": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                                 c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                                                                 c_int, c_float, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),
     "stride_paged_prefill_attention": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                             c_int, c_float, c_int, c_void_p]),
+                                                             c_int, c_float, c_int, c_float, c_void_p, c_void_p]),
     "stride_paged_prefill_attention_tc": ("attention_prefill_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                                   c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
+                                                                   c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "stride_sample_ranked": ("sampling_ranked", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_void_p, c_void_p, c_longlong, c_void_p]),
     "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -146,7 +149,7 @@ _CLASS_OF = {
     "stride_embed_gather": "embedding", "stride_add_rmsnorm": "norm", "stride_add_residual": "residual sum",
     "stride_scale_rows": "norm", "stride_zero_fresh_state": "state slots", "stride_rope_kv_write": "rotation + cache write",
     "stride_silu_mul": "silu * up", "stride_paged_attention_generic": "attention (exact kernel)",
-    "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
+    "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_decode_attention_rules": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
     "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling", "stride_sample_ranked": "sampling",
     "stride_add_dyt": "norm", "stride_add_scaled": "residual sum", "stride_token_side": "token side input",
     "stride_latent_prepare": "latent norm + rotation + cache write", "stride_head_gemm": "per-head product",
@@ -1062,10 +1065,8 @@ def paged_attention(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of
         _opt(sinks, "sinks", torch.float32), _code(q.dtype), _stream()), "paged_attention")
 
 
-def fast_attention_supported(dtype, nq: int, nkv: int, hd: int, softcap: float = 0.0, sinks: bool = False) -> bool:
-    """Sizes and rules that the tensor-core attention kernels run; others use the generic kernel."""
-    if softcap or sinks:
-        return False
+def fast_attention_supported(dtype, nq: int, nkv: int, hd: int) -> bool:
+    """Sizes that the tensor-core attention kernels run; others use the generic kernel."""
     return dtype == torch.bfloat16 and hd in (64, 128) and nq % nkv == 0 and nq // nkv <= 16
 
 
@@ -1081,26 +1082,29 @@ def decode_scratch_floats(tokens: int, nq: int, nkv: int, hd: int, max_context: 
 
 
 def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, scratch, nq: int,
-                           nkv: int, hd: int, page_size: int, scale: float, window: int, max_context: int) -> None:
+                           nkv: int, hd: int, page_size: int, scale: float, window: int, max_context: int, softcap: float = 0.0,
+                           sinks=None) -> None:
     """Attention for single decoded tokens (one query per row), split over the keys;
     ``scratch`` (float32, zero when first used) holds the ticket counters and the
-    partial results of the splits."""
+    partial results of the splits. ``softcap`` and ``sinks`` as for ``paged_attention``."""
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
-    _check(_fn("stride_paged_decode_attention_tma")(
+    _check(_fn("stride_paged_decode_attention_rules")(
         _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
-        int(max_context), _tc_buffers(q.device, 0)["status"].data_ptr(), _stream()), "paged_attention_decode")
+        float(softcap), _opt(sinks, "sinks", torch.float32), int(max_context), _tc_buffers(q.device, 0)["status"].data_ptr(), _stream()),
+        "paged_attention_decode")
 
 
 TC_ATTENTION = _os.environ.get("STRIDE_B200_TC_ATTENTION", "1") != "0"
 
 
 def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,
-                               nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int) -> bool:
+                               nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int, softcap: float = 0.0,
+                               sinks=None) -> bool:
     """The tcgen05 version of ``paged_attention_prefill`` (same arguments). Returns False
     when it does not take the sizes; the caller then uses the mma.sync kernel."""
     tokens = out.shape[0]
@@ -1111,8 +1115,8 @@ def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_ta
         _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
-        _dev(ctx_len, "ctx_len", torch.int32), num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window),
-        st["status"].data_ptr(), _stream())
+        _dev(ctx_len, "ctx_len", torch.int32), num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window), float(softcap),
+        _opt(sinks, "sinks", torch.float32), st["status"].data_ptr(), _stream())
     if code == -2:
         return False
     _check(code, "paged_attention_prefill_tc")
@@ -1120,9 +1124,10 @@ def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_ta
 
 
 def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,
-                            nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int) -> None:
+                            nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int, softcap: float = 0.0,
+                            sinks=None) -> None:
     """Attention for the first ``num_seqs`` requests of the step (portions of any
-    length), which own the rows of ``out``."""
+    length), which own the rows of ``out``. ``softcap`` and ``sinks`` as for ``paged_attention``."""
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
@@ -1130,7 +1135,8 @@ def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table
         _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(ctx_len, "ctx_len", torch.int32),
-        num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window), _stream()), "paged_attention_prefill")
+        num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window), float(softcap), _opt(sinks, "sinks", torch.float32),
+        _stream()), "paged_attention_prefill")
 
 
 # --------------------------------------------------------------------- sampling

@@ -38,9 +38,8 @@ class PagedAttention(Mixer):
         s = spec
         if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
             raise ValueError(f"{s.num_heads} query heads do not group into {s.num_kv_heads} KV heads")
-        if s.head_dim % 16 or s.head_dim > 256:
-            raise ValueError(f"head_dim {s.head_dim} is not supported by the attention kernels "
-                             "(multiples of 16 up to 256 are)")
+        if s.head_dim <= 0 or s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim} is not supported by the attention kernels (up to 256 is)")
         if s.window is not None and s.window <= 0:
             raise ValueError("an attention window must be positive")
         self.hidden = s.hidden
@@ -58,7 +57,7 @@ class PagedAttention(Mixer):
         permutation = getattr(self.position, "head_permutation", lambda: None)()
         self.perm = None if permutation is None else torch.tensor(permutation, dtype=torch.long)
         self.w_qkv = self.w_o = self.bias = self.w_gate = self.sinks = None
-        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd, self.softcap, self.has_sinks)
+        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd)
         self.accepts_folded = not self.gated          # the gate reads the normed input as a tensor
 
     # ----------------------------------------------------------------- weights
@@ -191,7 +190,7 @@ class PagedAttention(Mixer):
         split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
         if split > 0:
             args = (qkv[:split], self.qkv_dim, attn[:split], cache.k_pages, cache.v_pages, table, ctx.q_start, ctx.q_len,
-                    ctx.ctx_len, ctx.decode_tail_seq, *geometry)
+                    ctx.ctx_len, ctx.decode_tail_seq, *geometry, self.softcap, self.sinks)
             # tcgen05 kernel first; the mma.sync kernel takes what it refuses (odd page sizes)
             if not (ops.TC_ATTENTION and ops.paged_attention_prefill_tc(*args)):
                 ops.paged_attention_prefill(*args)
@@ -200,7 +199,7 @@ class PagedAttention(Mixer):
             scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.nkv, self.hd, ctx.context_bound))
             ops.paged_attention_decode(qkv[split:tokens], self.qkv_dim, attn[split:tokens], cache.k_pages, cache.v_pages, table,
                                        ctx.seq_of_token[split:tokens], ctx.positions[split:tokens], scratch, *geometry,
-                                       ctx.context_bound)
+                                       ctx.context_bound, self.softcap, self.sinks)
 
 
 register_part("mixer", "attention", PagedAttention)
