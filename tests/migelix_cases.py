@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import copy
 import math
 
 import torch
@@ -53,7 +54,7 @@ def config(width, vocab, layers, eps=1e-6, logit_softcap=None):
     out = []
     for entry in layers:
         if isinstance(entry, int):
-            out.append(dict(out[entry], weights_of=entry))
+            out.append(dict(copy.deepcopy(out[entry]), weights_of=entry))
         else:
             m, ff = entry
             out.append(dict(m, mlp={"kind": "dense", "ff": ff} if ff else None))
@@ -112,7 +113,8 @@ def seeded_state(cfg: dict, seed: int, sharp: float = 1.0, decay_rank: int = 6, 
     def vec(n, mean=0.0, std=0.3):
         return mean + std * torch.randn(n, generator=g)
 
-    s = {"embed": torch.randn(vocab, width, generator=g), "final.norm": vec(width, 0.0, 0.2)}
+    # the table is the head too: rows of norm about 2.5, so that logits stay within a few units
+    s = {"embed": torch.randn(vocab, width, generator=g) * (2.5 / math.sqrt(width)), "final.norm": vec(width, 0.0, 0.2)}
 
     def attn(p, m, biased, sinks, gated):
         h, kv, d = m["heads"], m["kv_heads"], m["dim"]
