@@ -383,7 +383,9 @@ def run_profile(args) -> dict:
     if args.compare:        # the compared design at the first of --compare-sizes instead of a Llama shape
         from stride_b200.config import config_from_dict
         full_layers = args.layers or 6
-        cfg = config_from_dict(compare_configs(COMPARE_SIZES[args.compare_sizes.split(",")[0]], full_layers)[0])
+        first = args.compare_sizes.split(",")[0]
+        cfg = config_from_dict(compare_configs_migelix(MIGELIX_SIZES[first], full_layers)[0] if args.compare == "migelix"
+                               else compare_configs(COMPARE_SIZES[first], full_layers)[0])
         vocab, layers = cfg.vocab, full_layers
     else:
         cfg, full_layers = bench_config(args.layers, args.shape)
@@ -451,6 +453,39 @@ def compare_configs(size: dict, layers: int):
     return ours, llama
 
 
+# Layer sizes for `--compare migelix`: layers cycle parallel (windowed attention with sinks beside a gated delta rule),
+# decayed memory, windowed attention with capped scores and an output gate; the dense feed-forward has the Llama
+# decoder's inner width, the attention layers its head size and grouping.
+MIGELIX_SIZES = {
+    "w1024": dict(width=1024, vocab=32000, ff=2752, heads=8, kv=2, dim=128, window=1024, delta_heads=8, delta_dim=128, memory_heads=16,
+                  memory_dim=64, decay_rank=64, gate_rank=128),
+    "w2048": dict(width=2048, vocab=32000, ff=5504, heads=16, kv=4, dim=128, window=1024, delta_heads=16, delta_dim=128, memory_heads=32,
+                  memory_dim=64, decay_rank=64, gate_rank=128),
+}
+
+
+def compare_configs_migelix(size: dict, layers: int):
+    """(Migelix config.json, Llama config.json) of one size."""
+    left = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
+            "mask": {"size": size["window"]},
+            "rot": {"base": 50000.0, "dims": size["dim"] // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": size["delta_heads"], "kv_heads": size["delta_heads"], "dim": size["delta_dim"], "vdim": size["delta_dim"], "conv": 4,
+             "decay_rank": size["decay_rank"], "gate_rank": size["gate_rank"]}
+    attention = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
+                 "mask": {"size": size["window"]}, "softcap": 50.0, "rot": {"base": 1e6, "dims": size["dim"]}}
+    memory = {"heads": size["memory_heads"], "dim": size["memory_dim"], "decay_rank": size["decay_rank"]}
+    kinds = [("parallel", {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}), ("wkv", memory), ("attention", attention)]
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    entries = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": mlp} for i in range(layers)]
+    ours = {"architecture": "Migelix", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-5}, "logit_softcap": 15.0,
+            "layers": entries}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "hidden_size": size["width"],
+             "num_attention_heads": size["heads"], "num_key_value_heads": size["kv"], "head_dim": size["dim"],
+             "intermediate_size": size["ff"], "vocab_size": size["vocab"], "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu"}
+    return ours, llama
+
+
 def _measure_design(config: dict, batch: int, context: int, prompt_len: int, steps: int, warmup: int) -> dict:
     """Prefill of one prompt and a decode step of ``batch`` requests at ``context`` for one configuration: device time
     by CUDA events, and the device time per class of kernel of one eagerly run step of each."""
@@ -507,15 +542,18 @@ def _measure_design(config: dict, batch: int, context: int, prompt_len: int, ste
 
 
 def run_compare(args) -> dict:
-    """``--compare nidilix``: prefill and decode throughput of the Nidilix design at a few layer sizes beside the Llama
-    decoder at equal size, with the device time per class of kernel. Not the headline workload."""
+    """``--compare nidilix | migelix``: prefill and decode throughput of that design at a few layer sizes beside the
+    Llama decoder at equal size, with the device time per class of kernel. Not the headline workload."""
     layers = args.layers or 6
     sizes = [s for s in args.compare_sizes.split(",") if s]
-    result = {"mode": "compare", "design": "nidilix", "beside": "llama", "layers": layers, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    result = {"mode": "compare", "design": args.compare, "beside": "llama", "layers": layers, "dtype": "bf16", "data": "synthetic", "sizes": {}}
     for name in sizes:
-        ours, llama = compare_configs(COMPARE_SIZES[name], layers)
+        if args.compare == "migelix":
+            ours, llama = compare_configs_migelix(MIGELIX_SIZES[name], layers)
+        else:
+            ours, llama = compare_configs(COMPARE_SIZES[name], layers)
         result["sizes"][name] = {
-            "nidilix": _measure_design(ours, args.batch, args.context, 2048, args.steps, args.warmup),
+            args.compare: _measure_design(ours, args.batch, args.context, 2048, args.steps, args.warmup),
             "llama": _measure_design(llama, args.batch, args.context, 2048, args.steps, args.warmup)}
     return result
 
@@ -616,7 +654,7 @@ def main(argv=None) -> int:
     p.add_argument("--no-breakdown", action="store_true", help="skip the per-class times of one decode step and the prefill")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="run a few eager steps of one kind for a profiler instead of measuring")
-    p.add_argument("--compare", choices=["nidilix"], default=None,
+    p.add_argument("--compare", choices=["nidilix", "migelix"], default=None,
                    help="instead of the headline workload: this design's prefill and decode beside the Llama decoder at equal size")
     p.add_argument("--compare-sizes", default="w1024,w2048", help="comma-separated names of the sizes to compare")
     args = p.parse_args(argv)

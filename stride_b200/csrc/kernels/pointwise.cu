@@ -7,6 +7,7 @@
 //   sigmoid_gate  x *= sigmoid(g)
 //   softcap       x = c tanh(x / c)            (float32, in place: logits)
 //   tanh_inplace  x = tanh(x)
+//   weighted_sum  out = sa * a + sb * b        (the sum of two branches; out may be a or b)
 #include "common.cuh"
 
 namespace stride {
@@ -110,6 +111,45 @@ __global__ void unary_kernel(T* __restrict__ x, const T* __restrict__ g, int op,
 }
 
 template <typename T>
+__global__ void weighted_sum_vec_kernel(T* out, const T* a, float sa, const T* b, float sb, size_t packs) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int V = Vec<T>::V;
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= packs) return;
+    Vec<T> x, y;
+    x.load(a + idx * V);
+    y.load(b + idx * V);
+#pragma unroll
+    for (int j = 0; j < V; ++j) x.v[j] = fmaf(sb, y.v[j], sa * x.v[j]);
+    x.store(out + idx * V);
+}
+
+template <typename T>
+__global__ void weighted_sum_kernel(T* out, const T* a, float sa, const T* b, float sb, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    out[idx] = from_f32<T>(fmaf(sb, to_f32(b[idx]), sa * to_f32(a[idx])));
+}
+
+template <typename T>
+int weighted(void* out, const void* a, float sa, const void* b, float sb, long long n, cudaStream_t stream) {
+    constexpr int V = Vec<T>::V;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
+    if (bits % 16 == 0 && n % V == 0) {
+        const size_t packs = static_cast<size_t>(n) / V;
+        stride::launch(weighted_sum_vec_kernel<T>, dim3(static_cast<unsigned>((packs + 127) / 128)), dim3(128), 0, stream, static_cast<T*>(out),
+                       static_cast<const T*>(a), sa, static_cast<const T*>(b), sb, packs);
+    } else {
+        stride::launch(weighted_sum_kernel<T>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream, static_cast<T*>(out),
+                       static_cast<const T*>(a), sa, static_cast<const T*>(b), sb, static_cast<size_t>(n));
+    }
+    return STRIDE_LAUNCH_STATUS();
+}
+
+template <typename T>
 int unary(void* x, const void* g, int op, float cap, long long n, cudaStream_t stream) {
     constexpr int V = Vec<T>::V;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g);
@@ -161,6 +201,15 @@ int stride_pointwise(void* x, const void* g, int op, float cap, long long n, int
     if (n == 0) return 0;
     if (dtype == STRIDE_DTYPE_F32) return unary<float>(x, g, op, cap, n, stream);
     if (dtype == STRIDE_DTYPE_BF16) return unary<__nv_bfloat16>(x, g, op, cap, n, stream);
+    return STRIDE_BAD_ARGUMENT;
+}
+
+int stride_weighted_sum(void* out, const void* a, float sa, const void* b, float sb, long long n, int dtype, cudaStream_t stream) {
+    if (n < 0) return STRIDE_BAD_ARGUMENT;
+    if (n / 4 / 128 > 0x7fffffffll) return STRIDE_UNSUPPORTED;
+    if (n == 0) return 0;
+    if (dtype == STRIDE_DTYPE_F32) return weighted<float>(out, a, sa, b, sb, n, stream);
+    if (dtype == STRIDE_DTYPE_BF16) return weighted<__nv_bfloat16>(out, a, sa, b, sb, n, stream);
     return STRIDE_BAD_ARGUMENT;
 }
 

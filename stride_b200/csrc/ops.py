@@ -37,7 +37,7 @@ _SIGNATURES = {
                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_gemm_tc_gated": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
-                                              c_void_p]),
+                                              c_int, c_void_p]),
     "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -115,6 +115,7 @@ _SIGNATURES = {
     "stride_relu_squared": ("moe", [c_void_p, c_longlong, c_int, c_void_p]),
     "stride_gated_act": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_pointwise": ("pointwise", [c_void_p, c_void_p, c_int, c_float, c_longlong, c_int, c_void_p]),
+    "stride_weighted_sum": ("pointwise", [c_void_p, c_void_p, c_float, c_void_p, c_float, c_longlong, c_int, c_void_p]),
     "stride_delta_prepare": ("linear_recurrence", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
                                                    c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
@@ -158,7 +159,7 @@ _CLASS_OF = {
     "stride_moe_select": "router", "stride_rglru_conv": "recurrent block: convolution",
     "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_rglru_scan_pieces": "recurrent block: recurrence", "stride_moe_route": "router",
     "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
-    "stride_relu_squared": "relu^2", "stride_gated_act": "act * up", "stride_pointwise": "gates and caps",
+    "stride_relu_squared": "relu^2", "stride_gated_act": "act * up", "stride_pointwise": "gates and caps", "stride_weighted_sum": "sum of branches",
     "stride_delta_prepare": "delta rule: convolution, unit vectors, decay", "stride_delta_scan": "delta rule: recurrence",
     "stride_bonus_scan": "decayed memory: recurrence", "stride_shift_mix": "decayed memory: token shift",
     "stride_head_norm_gate": "per-head norm and gate",
@@ -347,6 +348,14 @@ def sigmoid_gate(x, gate) -> None:
 def softcap_(x, cap: float) -> None:
     """``x = cap * tanh(x / cap)`` in place."""
     _check(_fn("stride_pointwise")(_dev(x, "x"), None, 1, float(cap), x.numel(), _code(x.dtype), _stream()), "softcap")
+
+
+def weighted_sum(out, a, sa: float, b, sb: float) -> None:
+    """``out = sa * a + sb * b`` elementwise, formed in float32 and rounded once; ``out`` may be ``a`` or ``b``."""
+    if not (out.shape == a.shape == b.shape and out.dtype == a.dtype == b.dtype):
+        raise KernelError("weighted_sum: one shape and one element type for all three")
+    _check(_fn("stride_weighted_sum")(_dev(out, "out"), _dev(a, "a"), float(sa), _dev(b, "b"), float(sb), out.numel(), _code(out.dtype),
+                                      _stream()), "weighted_sum")
 
 
 def tanh_(x) -> None:
@@ -948,8 +957,8 @@ def linear_add_norm(x, weight, residual, norm_weight, xt, partials) -> int:
     return count.value
 
 
-def linear_gated_tc(x, weight, out, folded=None) -> bool:
-    """``out = silu(x @ gate.T) * (x @ up.T)`` in one tcgen05 kernel for at most 16 rows of ``x``; ``weight`` is
+def linear_gated_tc(x, weight, out, folded=None, activation: str = "silu") -> bool:
+    """``out = act(x @ gate.T) * (x @ up.T)`` (``activation`` one of ``ACTIVATIONS``) in one tcgen05 kernel for at most 16 rows of ``x``; ``weight`` is
     [2 * inter, k] with gate and up rows alternating in blocks of ``GATED_BLOCK``. With ``folded`` (a FoldedNorm
     whose ``xt`` is ``x``) the kernel applies the norm's 1/rms itself. Returns False when the kernel does not take
     the sizes (the caller then runs the product and ``silu_mul`` with the same block)."""
@@ -959,9 +968,9 @@ def linear_gated_tc(x, weight, out, folded=None) -> bool:
         return False
     st = _tc_buffers(x.device, 0)
     partials, count, eps = _fold_args(folded)
-    code = _fn("stride_gemm_tc_gated", f"product 2x{inter}x{k} (tcgen05, silu * up)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
+    code = _fn("stride_gemm_tc_gated", f"product 2x{inter}x{k} (tcgen05, {activation} * up)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
                                        _dev(out, "out", torch.bfloat16), m, inter, k, st["status"].data_ptr(), partials, count, eps,
-                                       _stream())
+                                       ACTIVATIONS[activation], _stream())
     if code == -2:
         return False
     _check(code, "gemm_tc_gated")

@@ -4,7 +4,7 @@ theirs, ``sum_i scale_i * mixer_i(h)``.
 Spec params: ``branches``, a tuple of ``(MixerSpec, scale)``; each branch is built from the part registry by its own
 kind and finds its tensors under its own prefix. The branches share the run's cache slot: at most one of them may keep
 pages and at most one a state of fixed size (an attention beside a recurrence, say), so the cache manager sees one
-mixer. The sum is formed in float32 and handed on in the compute type.
+mixer. The sum is formed in float32, in one kernel, and handed on in the compute type.
 """
 
 from __future__ import annotations
@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Mixer, build_part, register_part
+from .base import Mixer, Projection, build_part, register_part
 
 
 class ParallelMixer(Mixer):
@@ -51,16 +51,25 @@ class ParallelMixer(Mixer):
 
     def forward(self, x, ctx, cache):
         tokens = x.shape[0]
-        total = self.rt.buffer("parallel_sum", tokens, self.hidden, torch.float32)
-        total.zero_()
-        for mixer, scale in self.branches:
-            # branch by branch: the branches' outputs may share a buffer
-            ops.add_scaled(total, mixer.forward(x, ctx, cache), scale)
-        if self.rt.dtype == torch.float32:
-            return total
-        result = self.rt.buffer("parallel_out", tokens, self.hidden)
-        ops.cast_rows(total, result)
-        return result
+        outs = []
+        for i, (mixer, _scale) in enumerate(self.branches):
+            # every branch's output in a buffer of this part's own: the branches' own output buffers may be one and the same
+            out = self.rt.buffer(f"parallel_branch{i}", tokens, self.hidden)
+            if mixer.lazy_output:
+                p = mixer.forward(x, ctx, cache, lazy_output=True)
+                if isinstance(p, Projection):
+                    ops.linear(p.x, p.weight, out)
+                else:
+                    out.copy_(p)
+            else:
+                out.copy_(mixer.forward(x, ctx, cache))
+            outs.append(out)
+        total = outs[0]
+        if len(outs) == 1:
+            ops.weighted_sum(total, outs[0], self.branches[0][1], outs[0], 0.0)
+        for i in range(1, len(outs)):
+            ops.weighted_sum(total, total, self.branches[0][1] if i == 1 else 1.0, outs[i], self.branches[i][1])
+        return total
 
 
 register_part("mixer", "parallel", ParallelMixer)

@@ -62,10 +62,11 @@ class SwiGLU(FeedForward):
         tokens = x.shape[0]
         act = self.rt.buffer("ffn_act", tokens, self.inter)
         folded = x if isinstance(x, ops.FoldedNorm) else None
-        # the products that apply the activation in their epilogue know SiLU only
-        gated = self.activation == "silu" and self.block == ops.GATED_BLOCK and (
-            ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded)
-            or (ops.rows_wanted(tokens) and ops.linear_rows_gated(folded.xt if folded else x, self.w_gate_up, act, folded)))
+        # the tcgen05 product for a few tokens applies either activation in its epilogue, the tokens-as-rows product SiLU only
+        gated = self.block == ops.GATED_BLOCK and (
+            ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded, self.activation)
+            or (self.activation == "silu" and ops.rows_wanted(tokens)
+                and ops.linear_rows_gated(folded.xt if folded else x, self.w_gate_up, act, folded)))
         if not gated:
             if folded:
                 x = folded.tensor()

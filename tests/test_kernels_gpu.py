@@ -315,12 +315,12 @@ def test_attention_f32_is_bitwise_the_same_for_a_token_alone_and_in_a_portion(op
 
 
 def test_kernels_refuse_sizes_they_cannot_run(ops):
-    q = torch.zeros(1, 24, device="cuda")
-    pages = torch.zeros(1, 1, 16, 24, device="cuda")
+    q = torch.zeros(1, 272, device="cuda")            # the exact kernel takes any head size up to 256
+    pages = torch.zeros(1, 1, 16, 272, device="cuda")
     table = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(ops.KernelError, match="not supported"):
-        ops.paged_attention(q, 24, torch.empty(1, 24, device="cuda"), pages, pages, table, z, z, 1, 1, 24, 16, 1.0, 0)
+        ops.paged_attention(q, 272, torch.empty(1, 272, device="cuda"), pages, pages, table, z, z, 1, 1, 272, 16, 1.0, 0)
     with pytest.raises(ops.KernelError, match="CUDA device"):
         ops.silu_mul(torch.zeros(1, 4), torch.zeros(1, 2))
 

@@ -100,6 +100,40 @@ def test_gelu_gate_times_up(gpu, dtype, tol, tokens, inter, block):
     close(out, gate.double() * torch.sigmoid(gate.double()) * up.double(), tol)
 
 
+@pytest.mark.parametrize("tokens,inter,k", [(8, 2752, 1024), (3, 9472, 192), (1, 5504, 2048)])
+def test_gelu_in_the_epilogue_of_the_gate_and_up_product(gpu, tokens, inter, k):
+    """The product for a few tokens that applies the activation itself, against the product followed by the kernel above."""
+    from stride_b200.csrc import ops
+    from stride_b200.parts.swiglu import interleave_gate_up
+    g = torch.Generator().manual_seed(inter)
+    x = torch.randn(tokens, k, generator=g).bfloat16().cuda()
+    gate, up = ((torch.randn(inter, k, generator=g) * 0.05).bfloat16() for _ in range(2))
+    w = interleave_gate_up(gate, up, ops.GATED_BLOCK).cuda()
+    out = torch.full((tokens, inter), 7.0, dtype=torch.bfloat16, device="cuda")
+    if not ops.linear_gated_tc(x, w, out, None, "gelu_tanh"):
+        pytest.skip("the tcgen05 product does not take these sizes")
+    both = torch.empty(tokens, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    ops.linear(x, w, both)
+    unfused = torch.empty_like(out)
+    ops.gated_act(both, unfused, ops.GATED_BLOCK, "gelu_tanh")
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    close(out, unfused, 1e-2)
+    gx = (x.double().cpu() @ gate.double().T).bfloat16().double()
+    ux = (x.double().cpu() @ up.double().T).bfloat16().double()
+    close(out, plain.gelu_tanh(gx) * ux, 1e-2)
+
+
+def test_parallel_branches_are_summed_with_their_weights(gpu):
+    from stride_b200.csrc import ops
+    g = torch.Generator().manual_seed(5)
+    for n, dtype in ((96, torch.bfloat16), (37, torch.float32)):
+        a, b = (torch.randn(4, n, generator=g).to(dtype) for _ in range(2))
+        out = a.cuda()
+        ops.weighted_sum(out, out, 0.6, b.cuda(), 1.3)
+        close(out, 0.6 * a.double() + 1.3 * b.double(), 1e-2 if dtype == torch.bfloat16 else 3e-6)
+
+
 def test_gates_caps_and_tanh_in_place(gpu):
     from stride_b200.csrc import ops
     g = torch.Generator().manual_seed(1)
