@@ -160,7 +160,8 @@ def cmd_plan(args) -> int:
     from .config import PlanError, config_from_dict, load_config, plan_memory, preset
 
     if args.model:
-        config = load_config(args.model)
+        from .engine.loading import read_config
+        config = read_config(args.model)
     else:
         config = config_from_dict(preset(args.preset) if args.preset else json.load(open(args.config)))
     try:

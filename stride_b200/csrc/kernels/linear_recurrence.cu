@@ -264,33 +264,34 @@ scan_kernel(const ScanArgs p) {
             const float vj = s_v[tt][jc];
             float out;
             if (RULE == 0) {
-                float dot = 0.f;
+                // four partial sums each (R is a multiple of 4): a single chain of R dependent additions would set the pace
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int i = il + kLanes * r;
                     S[r] = fmaf(S[r], s_w[tt][i], S[r]);
-                    dot = fmaf(S[r], s_k[tt][i], dot);
+                    d[r & 3] = fmaf(S[r], s_k[tt][i], d[r & 3]);
                 }
-                dot = quad_sum(dot);
+                const float dot = quad_sum((d[0] + d[1]) + (d[2] + d[3]));
                 const float u = s_beta[tt] * (vj - dot);
-                float acc = 0.f;
+                float a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int i = il + kLanes * r;
                     S[r] = fmaf(s_k[tt][i], u, S[r]);
-                    acc = fmaf(S[r], s_a[tt][i], acc);
+                    a[r & 3] = fmaf(S[r], s_a[tt][i], a[r & 3]);
                 }
-                out = quad_sum(acc);
+                out = quad_sum((a[0] + a[1]) + (a[2] + a[3]));
             } else {
-                float acc = 0.f;
+                float a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int i = il + kLanes * r;
                     const float kv = s_k[tt][i] * vj;
-                    acc = fmaf(s_a[tt][i], fmaf(s_bonus[i], kv, S[r]), acc);
+                    a[r & 3] = fmaf(s_a[tt][i], fmaf(s_bonus[i], kv, S[r]), a[r & 3]);
                     S[r] = fmaf(s_w[tt][i], S[r], S[r]) + kv;
                 }
-                out = quad_sum(acc);
+                out = quad_sum((a[0] + a[1]) + (a[2] + a[3]));
             }
             if (il == 0 && j < DV) p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j] = out;
         }

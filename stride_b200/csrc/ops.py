@@ -964,7 +964,7 @@ def linear_gated_tc(x, weight, out, folded=None, activation: str = "silu") -> bo
     the sizes (the caller then runs the product and ``silu_mul`` with the same block)."""
     m, k = x.shape
     inter = weight.shape[0] // 2
-    if m > TC_GEMM_MAX_TOKENS or out.shape != (m, inter):
+    if m > TC_GEMM_MAX_TOKENS or out.shape != (m, inter) or x.dtype != torch.bfloat16:
         return False
     st = _tc_buffers(x.device, 0)
     partials, count, eps = _fold_args(folded)

@@ -27,13 +27,20 @@ def build_model(config, source, dtype: str, device="cuda", token_capacity: int =
     return model
 
 
+def read_config(model_dir: str, source=None):
+    """The typed configuration of a model folder, completed from the checkpoint's tensor names and shapes where
+    config.json leaves something to them."""
+    source = source or SafetensorsSource(model_dir)
+    names = source.names()
+    return load_config(model_dir, tensor_names=names, tensor_shapes={n: tuple(source.describe(n)[0]) for n in names})
+
+
 def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda", token_capacity: int = 2048, row_capacity: int = 256,
                min_positions: int = 0):
     """``min_positions``: position tables for at least this many positions, where the configuration can give them
     (``with_max_positions``), even if the checkpoint names a shorter length."""
     source = SafetensorsSource(model_dir)
-    names = source.names()
-    config = load_config(model_dir, tensor_names=names, tensor_shapes={n: tuple(source.describe(n)[0]) for n in names})
+    config = read_config(model_dir, source)
     spec_positions = getattr(config, "max_position_embeddings", None)
     if min_positions and spec_positions is not None and spec_positions < min_positions and hasattr(config, "with_max_positions"):
         config = config.with_max_positions(min_positions)
