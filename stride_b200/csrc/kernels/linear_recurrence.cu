@@ -9,10 +9,11 @@
 //                        o_t = (S + diag(b) k_t v_t^T)^T r_t ;  S <- diag(w_t) S + k_t v_t^T
 //
 // Both are independent over the DV columns of S, and along a column the only coupling is one sum over D per read. The
-// scan kernel gives a column to four neighbouring lanes: lane l of the four holds rows l, l + 4, l + 8, ... in
-// registers (R rows, so D <= 4 R; rows beyond D carry zeros), sums its part and the four add up by two shuffles, always
-// in the same order. A CTA of 128 threads owns 32 columns of one head of one request and walks the request's tokens of
-// the step in order, 16 tokens' inputs staged in shared memory at a time. The order of every sum depends on the token
+// scan kernel gives a column to 4, 8 or 16 neighbouring lanes: each holds R of the rows in registers (groups of four
+// neighbouring rows; rows beyond D carry zeros), sums its part in four partial sums and the lanes add up by shuffles,
+// always in the same order. A CTA of 128 threads owns 32, 16 or 8 columns of one head of one request and walks the
+// request's tokens of the step in order; the inputs of 8 or 16 tokens are staged in shared memory at a time, the next ones
+// being fetched into registers meanwhile. The order of every sum depends on the token
 // only, so a token's output is bitwise the same in a whole prompt, in portions or decoded alone. State per request lives
 // in one float32 row of the mixer's state tensor: S [heads, D, DV], then whatever the mixer needs of the past inputs.
 //
@@ -180,15 +181,7 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ wei
 }
 
 // --------------------------------------------------------------------------------------------------------- scans
-constexpr int kLanes = 4;           // lanes that share a column's rows
-constexpr int kCols = 32;           // columns a CTA
-constexpr int kChunk = 16;          // tokens staged at a time
-
-__device__ __forceinline__ float quad_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    return v;
-}
+constexpr int kScanThreads = 128;
 
 struct ScanArgs {
     const void* a;          // queries (delta) / receptance (memory with bonus): [tokens, lda], head h at column (h / group) * D
@@ -211,96 +204,201 @@ struct ScanArgs {
     long long tail_off;
 };
 
-template <int R, int RULE>      // RULE 0: gated delta rule, 1: decayed memory with a bonus
-__global__ void __launch_bounds__(kCols * kLanes)
+// LANES lanes share a column, each with R of its rows (R a multiple of 4): D <= LANES * R. A thread works on NC columns
+// at once (COLS apart), CHUNK tokens are staged at a time. One token follows the other and a warp issues in order, so what
+// sets the pace of a prompt is the chain of dependent instructions a token costs a warp (shared-memory reads, the sums,
+// the shuffles), not the amount of arithmetic: the rows are spread over as many lanes as the head size allows, and the NC
+// columns of a thread are independent chains that fill one another's waits (they also share the reads of k, q and the decay).
+template <int LANES, int R, int NC, int CHUNK, int RULE>      // RULE 0: gated delta rule, 1: decayed memory with a bonus
+__global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const ScanArgs p) {
     pdl_trigger();
     pdl_wait();
-    constexpr int DP = R * kLanes;
-    __shared__ float s_a[kChunk][DP], s_k[kChunk][DP], s_w[kChunk][DP], s_v[kChunk][kCols], s_beta[kChunk], s_bonus[DP];
+    constexpr int DP = R * LANES;                           // rows with padding
+    constexpr int THREADS = kScanThreads;
+    constexpr int COLS = THREADS / LANES;                   // columns of one pass over the threads
+    constexpr int CTA_COLS = COLS * NC;                     // columns of this CTA
+    constexpr int ROW_ITEMS = CHUNK * DP / THREADS;         // entries of each [chunk, DP] array a thread fetches
+    constexpr int V_ITEMS = (CHUNK * CTA_COLS + THREADS - 1) / THREADS;
+    static_assert(R % 4 == 0 && (CHUNK * DP) % THREADS == 0 && CHUNK <= THREADS, "chunks are shared out evenly");
+    // two buffers: while the tokens of one chunk are worked through, the next chunk's inputs are on their way from
+    // global memory into registers; they are stored (the decay's exponentials applied) when the chunk is done
+    __shared__ __align__(16) float s_a[2][CHUNK][DP], s_k[2][CHUNK][DP], s_w[2][CHUNK][DP];
+    __shared__ float s_v[2][CHUNK][CTA_COLS], s_beta[2][CHUNK];
+    __shared__ __align__(16) float s_bonus[DP], s_w0[DP];
     const int seq = blockIdx.z, h = blockIdx.y;
     const int len = p.q_len[seq];
     if (len <= 0) return;
     const int start = p.q_start[seq];
-    const int il = threadIdx.x & (kLanes - 1), jc = threadIdx.x >> 2;
-    const int j = blockIdx.x * kCols + jc;
+    const int il = threadIdx.x & (LANES - 1), jc = threadIdx.x / LANES;
+    const int j0 = blockIdx.x * CTA_COLS + jc;              // this thread's columns: j0 + c * COLS
     const int D = p.D, DV = p.DV, H = p.H;
     const int hk = h / p.group;
     float* S_g = p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride + static_cast<size_t>(h) * D * DV;
-    float S[R];
+    // lane il of a column's lanes holds rows 4 LANES g + 4 il + e (g < R / 4, e < 4) in S[.][4 g + e]: four neighbouring rows
+    // are one 16-byte read of shared memory, and the lanes read consecutive 16 bytes
+    auto row_of = [&](int r) { return 4 * LANES * (r >> 2) + 4 * il + (r & 3); };
+    float S[NC][R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = il + kLanes * r;
-        S[r] = (i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
-    }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = row_of(r), j = j0 + c * COLS;
+            S[c][r] = (i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
+        }
     if (RULE == 1)
-        for (int i = threadIdx.x; i < DP; i += blockDim.x) s_bonus[i] = i < D ? p.bonus[h * D + i] : 0.f;
+        for (int i = threadIdx.x; i < DP; i += blockDim.x) {
+            s_bonus[i] = i < D ? p.bonus[h * D + i] : 0.f;
+            s_w0[i] = i < D ? p.w0[h * D + i] : 0.f;
+        }
 
-    for (int c0 = 0; c0 < len; c0 += kChunk) {
-        const int nt = min(kChunk, len - c0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * DP; idx += blockDim.x) {
+    float fa[ROW_ITEMS], fk[ROW_ITEMS], fw[ROW_ITEMS], fv[V_ITEMS], fb = 0.f;
+    auto fetch = [&](int c0) {          // the chunk from token c0 on, into registers (zeros past the request's end)
+#pragma unroll
+        for (int n = 0; n < ROW_ITEMS; ++n) {
+            const int idx = n * THREADS + threadIdx.x;
             const int tt = idx / DP, i = idx - tt * DP;
-            const size_t row = static_cast<size_t>(start + c0 + tt);
-            float a = 0.f, k = 0.f, w = 0.f;
-            if (i < D) {
-                a = load_any(p.a, row * p.lda + hk * D + i, p.in_bf16);
-                k = load_any(p.k, row * p.lda + hk * D + i, p.in_bf16);
-                w = p.w[row * H * D + h * D + i];
-                if (RULE == 1) w = expm1f(-expf(w + p.w0[h * D + i]));
+            fa[n] = fk[n] = fw[n] = 0.f;
+            if (c0 + tt < len && i < D) {
+                const size_t row = static_cast<size_t>(start + c0 + tt);
+                fa[n] = load_any(p.a, row * p.lda + hk * D + i, p.in_bf16);
+                fk[n] = load_any(p.k, row * p.lda + hk * D + i, p.in_bf16);
+                fw[n] = p.w[row * H * D + h * D + i];
             }
-            s_a[tt][i] = a;
-            s_k[tt][i] = k;
-            s_w[tt][i] = w;
         }
-        for (int idx = threadIdx.x; idx < nt * kCols; idx += blockDim.x) {
-            const int tt = idx / kCols, c = idx - tt * kCols;
-            const int col = blockIdx.x * kCols + c;
-            s_v[tt][c] = col < DV ? load_any(p.v, static_cast<size_t>(start + c0 + tt) * p.ldv + h * DV + col, p.in_bf16) : 0.f;
+#pragma unroll
+        for (int n = 0; n < V_ITEMS; ++n) {
+            const int idx = n * THREADS + threadIdx.x;
+            const int tt = idx / CTA_COLS, c = idx - tt * CTA_COLS;
+            const int col = blockIdx.x * CTA_COLS + c;
+            fv[n] = (tt < CHUNK && c0 + tt < len && col < DV)
+                        ? load_any(p.v, static_cast<size_t>(start + c0 + tt) * p.ldv + h * DV + col, p.in_bf16) : 0.f;
         }
-        if (RULE == 0 && threadIdx.x < nt) s_beta[threadIdx.x] = p.beta[static_cast<size_t>(start + c0 + threadIdx.x) * H + h];
-        __syncthreads();
+        if (RULE == 0 && threadIdx.x < CHUNK)
+            fb = c0 + threadIdx.x < len ? p.beta[static_cast<size_t>(start + c0 + threadIdx.x) * H + h] : 0.f;
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < ROW_ITEMS; ++n) {
+            const int idx = n * THREADS + threadIdx.x;
+            const int tt = idx / DP, i = idx - tt * DP;
+            float w = fw[n];
+            if (RULE == 1) w = i < D ? expm1f(-expf(w + s_w0[i])) : 0.f;
+            s_a[buf][tt][i] = fa[n];
+            s_k[buf][tt][i] = fk[n];
+            s_w[buf][tt][i] = w;
+        }
+#pragma unroll
+        for (int n = 0; n < V_ITEMS; ++n) {
+            const int idx = n * THREADS + threadIdx.x;
+            if (idx < CHUNK * CTA_COLS) s_v[buf][idx / CTA_COLS][idx % CTA_COLS] = fv[n];
+        }
+        if (RULE == 0 && threadIdx.x < CHUNK) s_beta[buf][threadIdx.x] = fb;
+    };
+
+    fetch(0);
+    __syncthreads();            // s_w0 is there
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int c0 = 0; c0 < len; c0 += CHUNK, buf ^= 1) {
+        const int nt = min(CHUNK, len - c0);
+        const bool more = c0 + CHUNK < len;
+        if (more) fetch(c0 + CHUNK);
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = s_v[tt][jc];
-            float out;
+            const float4* w4 = reinterpret_cast<const float4*>(&s_w[buf][tt][4 * il]);
+            const float4* k4 = reinterpret_cast<const float4*>(&s_k[buf][tt][4 * il]);
+            const float4* a4 = reinterpret_cast<const float4*>(&s_a[buf][tt][4 * il]);
+            float vj[NC], out[NC];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) vj[c] = s_v[buf][tt][jc + c * COLS];
+            // four partial sums a read (fixed order): a single chain of R dependent additions would set the pace
             if (RULE == 0) {
-                // four partial sums each (R is a multiple of 4): a single chain of R dependent additions would set the pace
-                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                float d[NC][4], kk[R];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = il + kLanes * r;
-                    S[r] = fmaf(S[r], s_w[tt][i], S[r]);
-                    d[r & 3] = fmaf(S[r], s_k[tt][i], d[r & 3]);
-                }
-                const float dot = quad_sum((d[0] + d[1]) + (d[2] + d[3]));
-                const float u = s_beta[tt] * (vj - dot);
-                float a[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int c = 0; c < NC; ++c) d[c][0] = d[c][1] = d[c][2] = d[c][3] = 0.f;
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = il + kLanes * r;
-                    S[r] = fmaf(s_k[tt][i], u, S[r]);
-                    a[r & 3] = fmaf(S[r], s_a[tt][i], a[r & 3]);
+                for (int g = 0; g < R / 4; ++g) {
+                    const float4 w = w4[LANES * g], k = k4[LANES * g];
+                    const float wv[4] = {w.x, w.y, w.z, w.w};
+                    kk[4 * g] = k.x; kk[4 * g + 1] = k.y; kk[4 * g + 2] = k.z; kk[4 * g + 3] = k.w;
+#pragma unroll
+                    for (int c = 0; c < NC; ++c)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            S[c][4 * g + e] = fmaf(S[c][4 * g + e], wv[e], S[c][4 * g + e]);
+                            d[c][e] = fmaf(S[c][4 * g + e], kk[4 * g + e], d[c][e]);
+                        }
                 }
-                out = quad_sum((a[0] + a[1]) + (a[2] + a[3]));
+                float u[NC];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) u[c] = (d[c][0] + d[c][1]) + (d[c][2] + d[c][3]);
+#pragma unroll
+                for (int o = 1; o < LANES; o <<= 1)
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) u[c] += __shfl_xor_sync(0xffffffffu, u[c], o);
+                const float beta = s_beta[buf][tt];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) u[c] = beta * (vj[c] - u[c]);
+                float acc[NC][4];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+#pragma unroll
+                for (int g = 0; g < R / 4; ++g) {
+                    const float4 q = a4[LANES * g];
+                    const float qv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int c = 0; c < NC; ++c)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            S[c][4 * g + e] = fmaf(kk[4 * g + e], u[c], S[c][4 * g + e]);
+                            acc[c][e] = fmaf(S[c][4 * g + e], qv[e], acc[c][e]);
+                        }
+                }
+#pragma unroll
+                for (int c = 0; c < NC; ++c) out[c] = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
             } else {
-                float a[4] = {0.f, 0.f, 0.f, 0.f};
+                const float4* b4 = reinterpret_cast<const float4*>(&s_bonus[4 * il]);
+                float acc[NC][4];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = il + kLanes * r;
-                    const float kv = s_k[tt][i] * vj;
-                    a[r & 3] = fmaf(s_a[tt][i], fmaf(s_bonus[i], kv, S[r]), a[r & 3]);
-                    S[r] = fmaf(s_w[tt][i], S[r], S[r]) + kv;
+                for (int c = 0; c < NC; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+#pragma unroll
+                for (int g = 0; g < R / 4; ++g) {
+                    const float4 w = w4[LANES * g], k = k4[LANES * g], rr = a4[LANES * g], b = b4[LANES * g];
+                    const float wv[4] = {w.x, w.y, w.z, w.w}, kv4[4] = {k.x, k.y, k.z, k.w}, rv[4] = {rr.x, rr.y, rr.z, rr.w},
+                                bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int c = 0; c < NC; ++c)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float kv = kv4[e] * vj[c];
+                            acc[c][e] = fmaf(rv[e], fmaf(bv[e], kv, S[c][4 * g + e]), acc[c][e]);
+                            S[c][4 * g + e] = fmaf(wv[e], S[c][4 * g + e], S[c][4 * g + e]) + kv;
+                        }
                 }
-                out = quad_sum((a[0] + a[1]) + (a[2] + a[3]));
+#pragma unroll
+                for (int c = 0; c < NC; ++c) out[c] = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
             }
-            if (il == 0 && j < DV) p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j] = out;
+#pragma unroll
+            for (int o = 1; o < LANES; o <<= 1)
+#pragma unroll
+                for (int c = 0; c < NC; ++c) out[c] += __shfl_xor_sync(0xffffffffu, out[c], o);
+            if (il == 0) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c)
+                    if (j0 + c * COLS < DV) p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j0 + c * COLS] = out[c];
+            }
         }
+        if (more) stash(buf ^ 1);       // nobody reads that buffer: its chunk was finished before the last barrier
+        __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = il + kLanes * r;
-        if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[r];
-    }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = row_of(r), j = j0 + c * COLS;
+            if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[c][r];
+        }
     // The convolution's tail: row m of the new tail is the input of local token len - (taps - 1) + m, which lies in
     // this step or, for a short step, further up in the old tail. Channels are shared out over the CTAs of the request;
     // a channel's rows move in ascending order, so a row is read before it is overwritten.
@@ -317,18 +415,27 @@ scan_kernel(const ScanArgs p) {
     }
 }
 
+template <int LANES, int R, int CHUNK, int RULE>
+int launch_scan_as(const ScanArgs& p, int num_seqs, cudaStream_t stream) {
+    constexpr int COLS = kScanThreads / LANES;
+    // four columns a thread where the head is wide enough to fill them
+    if (p.DV >= 4 * COLS) {
+        const dim3 grid((p.DV + 4 * COLS - 1) / (4 * COLS), p.H, num_seqs);
+        stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE>, grid, dim3(kScanThreads), 0, stream, p);
+    } else {
+        const dim3 grid((p.DV + COLS - 1) / COLS, p.H, num_seqs);
+        stride::launch(scan_kernel<LANES, R, 1, CHUNK, RULE>, grid, dim3(kScanThreads), 0, stream, p);
+    }
+    return STRIDE_LAUNCH_STATUS();
+}
+
 template <int RULE>
 int launch_scan(const ScanArgs& p, int num_seqs, cudaStream_t stream) {
-    const dim3 grid((p.DV + kCols - 1) / kCols, p.H, num_seqs), block(kCols * kLanes);
-    const int rows = (p.D + kLanes - 1) / kLanes;
-    if (rows <= 4) stride::launch(scan_kernel<4, RULE>, grid, block, 0, stream, p);
-    else if (rows <= 8) stride::launch(scan_kernel<8, RULE>, grid, block, 0, stream, p);
-    else if (rows <= 12) stride::launch(scan_kernel<12, RULE>, grid, block, 0, stream, p);
-    else if (rows <= 16) stride::launch(scan_kernel<16, RULE>, grid, block, 0, stream, p);
-    else if (rows <= 24) stride::launch(scan_kernel<24, RULE>, grid, block, 0, stream, p);
-    else if (rows <= 32) stride::launch(scan_kernel<32, RULE>, grid, block, 0, stream, p);
-    else return STRIDE_UNSUPPORTED;
-    return STRIDE_LAUNCH_STATUS();
+    if (p.D <= 16) return launch_scan_as<4, 4, 16, RULE>(p, num_seqs, stream);
+    if (p.D <= 32) return launch_scan_as<8, 4, 16, RULE>(p, num_seqs, stream);
+    if (p.D <= 64) return launch_scan_as<16, 4, 16, RULE>(p, num_seqs, stream);
+    if (p.D <= 128) return launch_scan_as<16, 8, 8, RULE>(p, num_seqs, stream);
+    return STRIDE_UNSUPPORTED;
 }
 
 }  // namespace stride
