@@ -202,6 +202,13 @@ struct ScanArgs {
     const void* proj;
     int ld_proj, C, taps, proj_bf16;
     long long tail_off;
+    // pieces (mode 0: none, a request's tokens in one chain). A piece is `piece` consecutive tokens of a request; grid z is
+    // request * max_pieces + piece. Mode 1 runs every piece from a zero memory, writes no output, and leaves the piece's
+    // memory in piece_s [z, H, D, DV] and the product of its decays in piece_p [z, H, D]; mode 2 runs every piece from
+    // piece_s (by then the memory at the piece's start), writes the outputs and leaves the state alone.
+    int mode, piece, max_pieces;
+    float* piece_s;
+    float* piece_p;
 };
 
 // LANES lanes share a column, each with R of its rows (R a multiple of 4): D <= LANES * R. A thread works on NC columns
@@ -226,15 +233,17 @@ scan_kernel(const ScanArgs p) {
     __shared__ __align__(16) float s_a[2][CHUNK][DP], s_k[2][CHUNK][DP], s_w[2][CHUNK][DP];
     __shared__ float s_v[2][CHUNK][CTA_COLS], s_beta[2][CHUNK];
     __shared__ __align__(16) float s_bonus[DP], s_w0[DP];
-    const int seq = blockIdx.z, h = blockIdx.y;
-    const int len = p.q_len[seq];
-    if (len <= 0) return;
+    const int seq = p.mode ? blockIdx.z / p.max_pieces : blockIdx.z, h = blockIdx.y;
+    const int first = p.mode ? (blockIdx.z % p.max_pieces) * p.piece : 0;         // this CTA's tokens of the request: [first, len)
+    const int len = p.mode ? min(p.q_len[seq], first + p.piece) : p.q_len[seq];
+    if (len <= first) return;
     const int start = p.q_start[seq];
     const int il = threadIdx.x & (LANES - 1), jc = threadIdx.x / LANES;
     const int j0 = blockIdx.x * CTA_COLS + jc;              // this thread's columns: j0 + c * COLS
     const int D = p.D, DV = p.DV, H = p.H;
     const int hk = h / p.group;
-    float* S_g = p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride + static_cast<size_t>(h) * D * DV;
+    float* S_g = p.mode ? p.piece_s + (static_cast<size_t>(blockIdx.z) * H + h) * D * DV
+                        : p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride + static_cast<size_t>(h) * D * DV;
     // lane il of a column's lanes holds rows 4 LANES g + 4 il + e (g < R / 4, e < 4) in S[.][4 g + e]: four neighbouring rows
     // are one 16-byte read of shared memory, and the lanes read consecutive 16 bytes
     auto row_of = [&](int r) { return 4 * LANES * (r >> 2) + 4 * il + (r & 3); };
@@ -244,8 +253,11 @@ scan_kernel(const ScanArgs p) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int i = row_of(r), j = j0 + c * COLS;
-            S[c][r] = (i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
+            S[c][r] = (p.mode != 1 && i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
         }
+    float decayed[R];           // mode 1: the product of the decays of this thread's rows over the piece
+#pragma unroll
+    for (int r = 0; r < R; ++r) decayed[r] = 1.f;
     if (RULE == 1)
         for (int i = threadIdx.x; i < DP; i += blockDim.x) {
             s_bonus[i] = i < D ? p.bonus[h * D + i] : 0.f;
@@ -296,12 +308,12 @@ scan_kernel(const ScanArgs p) {
         if (RULE == 0 && threadIdx.x < CHUNK) s_beta[buf][threadIdx.x] = fb;
     };
 
-    fetch(0);
+    fetch(first);
     __syncthreads();            // s_w0 is there
     stash(0);
     __syncthreads();
     int buf = 0;
-    for (int c0 = 0; c0 < len; c0 += CHUNK, buf ^= 1) {
+    for (int c0 = first; c0 < len; c0 += CHUNK, buf ^= 1) {
         const int nt = min(CHUNK, len - c0);
         const bool more = c0 + CHUNK < len;
         if (more) fetch(c0 + CHUNK);
@@ -367,6 +379,10 @@ scan_kernel(const ScanArgs p) {
                     const float4 w = w4[LANES * g], k = k4[LANES * g], rr = a4[LANES * g], b = b4[LANES * g];
                     const float wv[4] = {w.x, w.y, w.z, w.w}, kv4[4] = {k.x, k.y, k.z, k.w}, rv[4] = {rr.x, rr.y, rr.z, rr.w},
                                 bv[4] = {b.x, b.y, b.z, b.w};
+                    if (p.mode == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) decayed[4 * g + e] = fmaf(wv[e], decayed[4 * g + e], decayed[4 * g + e]);
+                    }
 #pragma unroll
                     for (int c = 0; c < NC; ++c)
 #pragma unroll
@@ -383,7 +399,7 @@ scan_kernel(const ScanArgs p) {
             for (int o = 1; o < LANES; o <<= 1)
 #pragma unroll
                 for (int c = 0; c < NC; ++c) out[c] += __shfl_xor_sync(0xffffffffu, out[c], o);
-            if (il == 0) {
+            if (il == 0 && p.mode != 1) {
 #pragma unroll
                 for (int c = 0; c < NC; ++c)
                     if (j0 + c * COLS < DV) p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j0 + c * COLS] = out[c];
@@ -392,6 +408,7 @@ scan_kernel(const ScanArgs p) {
         if (more) stash(buf ^ 1);       // nobody reads that buffer: its chunk was finished before the last barrier
         __syncthreads();
     }
+    if (p.mode == 2) return;
 #pragma unroll
     for (int c = 0; c < NC; ++c)
 #pragma unroll
@@ -399,6 +416,14 @@ scan_kernel(const ScanArgs p) {
             const int i = row_of(r), j = j0 + c * COLS;
             if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[c][r];
         }
+    if (p.mode == 1) {
+        if (blockIdx.x == 0 && jc == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (row_of(r) < D) p.piece_p[(static_cast<size_t>(blockIdx.z) * H + h) * D + row_of(r)] = decayed[r];
+        }
+        return;
+    }
     // The convolution's tail: row m of the new tail is the input of local token len - (taps - 1) + m, which lies in
     // this step or, for a short step, further up in the old tail. Channels are shared out over the CTAs of the request;
     // a channel's rows move in ascending order, so a row is read before it is overwritten.
@@ -415,10 +440,40 @@ scan_kernel(const ScanArgs p) {
     }
 }
 
+// Between the two passes over pieces, for a memory whose decay is diagonal: piece_s [z, H, D, DV] holds what every piece
+// adds from a zero memory, piece_p [z, H, D] the product of its decays. One thread an entry of S walks the request's pieces
+// in order: the memory at a piece's start takes the place of the piece's own sum, and the memory after the last piece goes
+// into the state.
+__global__ void __launch_bounds__(256)
+pieces_combine_kernel(float* __restrict__ piece_s, const float* __restrict__ piece_p, float* __restrict__ state, long long state_stride,
+                      const int32_t* __restrict__ q_len, const int32_t* __restrict__ state_slot, int H, int D, int DV, int piece,
+                      int max_pieces) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.y;
+    const int len = q_len[seq];
+    if (len <= 0) return;
+    const int entry = blockIdx.x * blockDim.x + threadIdx.x;          // over H * D * DV
+    if (entry >= H * D * DV) return;
+    const int row = entry / DV;                                          // h * D + i
+    float* S_g = state + static_cast<size_t>(state_slot[seq]) * state_stride + entry;
+    float S = *S_g;
+    const int pieces = (len + piece - 1) / piece;
+    for (int c = 0; c < pieces; ++c) {
+        const size_t z = static_cast<size_t>(seq) * max_pieces + c;
+        float* at = piece_s + z * H * D * DV + entry;
+        const float own = *at;
+        *at = S;
+        S = fmaf(piece_p[z * H * D + row], S, own);
+    }
+    *S_g = S;
+}
+
 template <int LANES, int R, int CHUNK, int RULE>
 int launch_scan_as(const ScanArgs& p, int num_seqs, cudaStream_t stream) {
     constexpr int COLS = kScanThreads / LANES;
     // four columns a thread where the head is wide enough to fill them
+    if (p.mode) num_seqs *= p.max_pieces;
     if (p.DV >= 4 * COLS) {
         const dim3 grid((p.DV + 4 * COLS - 1) / (4 * COLS), p.H, num_seqs);
         stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE>, grid, dim3(kScanThreads), 0, stream, p);
@@ -505,10 +560,14 @@ int stride_delta_scan(const float* qk, const float* v, const float* beta, const 
 
 // Decayed memory with a bonus. r, k, v [tokens, H * D] in the compute type (one head size for keys and values);
 // wlog [tokens, H * D] float32: the decay is exp(-exp(wlog + w0)).
+// piece > 0: the recurrence in pieces of that many tokens, parallel over the pieces (three launches: every piece from a zero
+// memory; the memories at the pieces' starts; every piece from its start). scratch: float32, at least
+// num_seqs * max_pieces * H * D * (D + 1), max_pieces = ceil(longest portion / piece). The sums then take another order than
+// the single chain's, so the result depends on the cutting in the last bits: for bfloat16 runs and long portions.
 int stride_bonus_scan(const void* r, const void* k, const void* v, const float* wlog, const float* w0, const float* bonus, float* o,
                       float* state, long long state_stride, const int32_t* q_start, const int32_t* q_len, const int32_t* state_slot,
-                      int num_seqs, int H, int D, int dtype, cudaStream_t stream) {
-    if (num_seqs < 0 || H <= 0 || D <= 0) return STRIDE_BAD_ARGUMENT;
+                      int num_seqs, int H, int D, int dtype, int piece, int max_pieces, float* scratch, cudaStream_t stream) {
+    if (num_seqs < 0 || H <= 0 || D <= 0 || piece < 0 || (piece > 0 && (max_pieces <= 0 || scratch == nullptr))) return STRIDE_BAD_ARGUMENT;
     if (dtype != STRIDE_DTYPE_F32 && dtype != STRIDE_DTYPE_BF16) return STRIDE_BAD_ARGUMENT;
     if (num_seqs == 0) return 0;
     ScanArgs p = {};
@@ -532,6 +591,20 @@ int stride_bonus_scan(const void* r, const void* k, const void* v, const float* 
     p.DV = D;
     p.in_bf16 = dtype == STRIDE_DTYPE_BF16 ? 1 : 0;
     p.taps = 0;
+    if (piece == 0) return launch_scan<1>(p, num_seqs, stream);
+    p.piece = piece;
+    p.max_pieces = max_pieces;
+    p.piece_s = scratch;
+    p.piece_p = scratch + static_cast<size_t>(num_seqs) * max_pieces * H * D * D;
+    p.mode = 1;
+    int code = launch_scan<1>(p, num_seqs, stream);
+    if (code != 0) return code;
+    const int entries = H * D * D;
+    stride::launch(pieces_combine_kernel, dim3((entries + 255) / 256, num_seqs), dim3(256), 0, stream, p.piece_s,
+                   static_cast<const float*>(p.piece_p), state, state_stride, q_len, state_slot, H, D, D, piece, max_pieces);
+    code = STRIDE_LAUNCH_STATUS();
+    if (code != 0) return code;
+    p.mode = 2;
     return launch_scan<1>(p, num_seqs, stream);
 }
 

@@ -123,7 +123,7 @@ _SIGNATURES = {
                                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                 c_void_p]),
     "stride_bonus_scan": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
-                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_shift_mix": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_head_norm_gate": ("linear_recurrence", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
@@ -392,16 +392,30 @@ def delta_scan(qk, v, beta, decay, o, state, tail_off: int, proj, q_start, q_len
         G, H, D, DV, taps, _code(proj.dtype), _stream()), "delta_scan")
 
 
-def bonus_scan(r, k, v, wlog, w0, bonus, o, state, q_start, q_len, state_slot, num_seqs: int, H: int, D: int) -> None:
+MEMORY_PIECE = 64       # tokens a piece when a decayed memory runs its portions in pieces
+
+
+def bonus_scan_scratch_floats(num_seqs: int, max_q_len: int, H: int, D: int) -> int:
+    return num_seqs * -(-max_q_len // MEMORY_PIECE) * H * D * (D + 1)
+
+
+def bonus_scan(r, k, v, wlog, w0, bonus, o, state, q_start, q_len, state_slot, num_seqs: int, H: int, D: int, max_q_len: int = 0,
+               scratch=None) -> None:
     """Decayed memory with a bonus for the current token: ``o_t = (S + diag(bonus) k v^T)^T r``, then
-    ``S = diag(exp(-exp(wlog + w0))) S + k v^T``; r, k, v [tokens, H * D] in one element type, the rest float32."""
+    ``S = diag(exp(-exp(wlog + w0))) S + k v^T``; r, k, v [tokens, H * D] in one element type, the rest float32. With
+    ``scratch`` (float32, ``bonus_scan_scratch_floats`` for the step's longest portion ``max_q_len``) the portions run in
+    pieces of ``MEMORY_PIECE`` tokens, parallel over the pieces."""
     if not (r.dtype == k.dtype == v.dtype):
         raise KernelError("bonus_scan: r, k and v must have one element type")
+    piece = MEMORY_PIECE if scratch is not None else 0
+    max_pieces = -(-max_q_len // MEMORY_PIECE) if piece else 0
+    if piece and (max_pieces <= 0 or scratch.numel() < bonus_scan_scratch_floats(num_seqs, max_q_len, H, D)):
+        raise KernelError("bonus_scan: the scratch is too small")
     _check(_fn("stride_bonus_scan")(
         _dev(r, "r"), _dev(k, "k"), _dev(v, "v"), _dev(wlog, "wlog", torch.float32), _dev(w0, "w0", torch.float32),
         _dev(bonus, "bonus", torch.float32), _dev(o, "o", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
         _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32), num_seqs,
-        H, D, _code(r.dtype), _stream()), "bonus_scan")
+        H, D, _code(r.dtype), piece, max_pieces, _opt(scratch, "scratch", torch.float32), _stream()), "bonus_scan")
 
 
 def shift_mix(x, mu, state, prev_off: int, seq_of_token, q_start, q_len, state_slot, out) -> None:

@@ -202,7 +202,14 @@ class BonusMemoryMixer(Mixer):
         wlog = self.rt.buffer("wkv_wlog", tokens, self.HD, f32)
         ops.linear(low, self.w_2, wlog)
         o = self.rt.buffer("wkv_o", tokens, self.HD, f32)
-        ops.bonus_scan(r, k, v, wlog, self.w0, self.bonus, o, state, ctx.q_start, ctx.q_len, ctx.state_slot, ctx.q_len.shape[0], self.H, self.D)
+        seqs, scratch = ctx.q_len.shape[0], None
+        if x.dtype == torch.bfloat16 and ctx.max_q_len >= ops.SCAN_PIECES_MIN_TOKENS:
+            # a long portion: the recurrence in pieces, parallel over the pieces (the 32-bit path keeps the one chain, whose
+            # sums do not depend on the cutting)
+            seqs = ctx.num_seqs
+            scratch = self.rt.scratch("wkv_pieces", ops.bonus_scan_scratch_floats(seqs, ctx.max_q_len, self.H, self.D))
+        ops.bonus_scan(r, k, v, wlog, self.w0, self.bonus, o, state, ctx.q_start, ctx.q_len, ctx.state_slot, seqs, self.H, self.D,
+                       ctx.max_q_len, scratch)
         mixed = self.rt.buffer("wkv_mixed", tokens, self.HD)
         ops.head_norm_gate(o, self.norm_w, True, gate, "silu", mixed, self.H, self.D, self.norm_eps)
         if lazy_output:

@@ -374,6 +374,20 @@ def test_sharp_attention_and_long_decoding_past_the_window(gpu, tmp_models, dtyp
     replay(folder, dtype, modes.tail_one_by_one(requests, tail=120), want, 16, 2, "long decode", min_ok=share)
 
 
+def test_the_memory_in_pieces_gives_the_chain(gpu, tmp_models, monkeypatch):
+    """bfloat16, portions long enough for the recurrence in pieces (and a batch of two of them with a short one between):
+    against the plain chain, with portions that end inside pieces and a slot that is used again."""
+    from stride_b200.csrc import ops
+    cfg = cases.config(64, 101, [(cases.wkv(3, 20), None), (cases.wkv(1, 64), 48), (cases.wkv(2, 128), None)])
+    folder, requests, want = model_case(tmp_models, "pieces", cfg, "bfloat16", 31, [300, 70, 261])
+    monkeypatch.setattr(ops, "SCAN_PIECES_MIN_TOKENS", 128)
+    together = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": [0, len(t) // 2, len(t) - 1]} for r, t in requests.items()],
+                 "end": list(requests)}]
+    replay(folder, "bfloat16", together, want, 16, 3, "three prompts in one step", min_ok=0.97)
+    steps = modes.restrict_wants(modes.changing_portions(requests, sizes=(130, 2, 140, 65)), {r: set(range(0, len(t), 5)) for r, t in requests.items()})
+    replay(folder, "bfloat16", steps, want, 16, 1, "portions across the pieces' borders", min_ok=0.97)
+
+
 # --------------------------------------------------------------------------- generation through the engine
 def test_greedy_generation_through_the_engine(gpu, tmp_models):
     from stride_b200 import Engine, SamplingParams
