@@ -408,11 +408,23 @@ __global__ void rope_kv_write_pack_kernel(T* __restrict__ qkv, const float* __re
     Pack<T> a, b;
     a.load(x + i);
     b.load(x + i + half);
-    if (bias) {
+    if (bias) {     // i is a multiple of V and half of 4: 16-byte reads where the vector itself starts on such a boundary
+        if ((reinterpret_cast<uintptr_t>(bias) & 15) == 0 && hd % 4 == 0) {
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-            a.v[j] = __fadd_rn(a.v[j], bias[head * hd + i + j]);
-            b.v[j] = __fadd_rn(b.v[j], bias[head * hd + i + half + j]);
+            for (int j = 0; j < V; j += 4) {
+                const float4 x = *reinterpret_cast<const float4*>(bias + head * hd + i + j);
+                const float4 y = *reinterpret_cast<const float4*>(bias + head * hd + i + half + j);
+                a.v[j] = __fadd_rn(a.v[j], x.x); a.v[j + 1] = __fadd_rn(a.v[j + 1], x.y);
+                a.v[j + 2] = __fadd_rn(a.v[j + 2], x.z); a.v[j + 3] = __fadd_rn(a.v[j + 3], x.w);
+                b.v[j] = __fadd_rn(b.v[j], y.x); b.v[j + 1] = __fadd_rn(b.v[j + 1], y.y);
+                b.v[j + 2] = __fadd_rn(b.v[j + 2], y.z); b.v[j + 3] = __fadd_rn(b.v[j + 3], y.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                a.v[j] = __fadd_rn(a.v[j], bias[head * hd + i + j]);
+                b.v[j] = __fadd_rn(b.v[j], bias[head * hd + i + half + j]);
+            }
         }
     }
     if (turns) {

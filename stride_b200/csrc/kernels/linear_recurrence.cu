@@ -490,6 +490,7 @@ int launch_scan(const ScanArgs& p, int num_seqs, cudaStream_t stream) {
     if (p.D <= 32) return launch_scan_as<8, 4, 16, RULE>(p, num_seqs, stream);
     if (p.D <= 64) return launch_scan_as<16, 4, 16, RULE>(p, num_seqs, stream);
     if (p.D <= 128) return launch_scan_as<16, 8, 8, RULE>(p, num_seqs, stream);
+    if (p.D <= 256) return launch_scan_as<16, 16, 4, RULE>(p, num_seqs, stream);
     return STRIDE_UNSUPPORTED;
 }
 

@@ -53,8 +53,8 @@ class GatedDeltaMixer(Mixer):
             raise ValueError(f"{self.H} heads do not group into {self.G} q/k heads")
         if self.ra <= 0 or self.rg <= 0:
             raise ValueError("the gated delta rule needs decay_rank and gate_rank (read off the checkpoint, or given in the configuration)")
-        if self.D > 128 or self.DV > 256 or not 1 <= self.taps <= 16:
-            raise ValueError(f"sizes not supported by the recurrence kernels: dim {self.D} (up to 128), vdim {self.DV} (up to 256), "
+        if self.D > 256 or self.DV > 256 or not 1 <= self.taps <= 16:
+            raise ValueError(f"sizes not supported by the recurrence kernels: dim {self.D} (up to 256), vdim {self.DV} (up to 256), "
                              f"{self.taps} taps (1 to 16)")
         self.GD, self.HD, self.HV = self.G * self.D, self.H * self.D, self.H * self.DV
         self.C = 2 * self.GD + self.HV                       # channels that pass the convolution
@@ -146,8 +146,8 @@ class BonusMemoryMixer(Mixer):
             raise ValueError("the mixer needs positive heads and dim")
         if self.rw <= 0:
             raise ValueError("the mixer needs decay_rank (read off the checkpoint, or given in the configuration)")
-        if self.D > 128:
-            raise ValueError(f"dim {self.D} is not supported by the recurrence kernels (up to 128 is)")
+        if self.D > 256:
+            raise ValueError(f"dim {self.D} is not supported by the recurrence kernels (up to 256 is)")
         self.HD = self.H * self.D
         self.r_pad = _pad8(self.rw)
         self.s_floats = self.H * self.D * self.D

@@ -251,8 +251,9 @@ def test_tensor_core_attention_with_caps_and_sinks_against_the_exact_kernel(gpu,
 
 # ------------------------------------------------------------------- each mixer in a model of nothing else
 ONLY_DELTA = cases.config(72, 101, [(cases.parallel(cases.attn_sizes(1, 1, 16, cases.rot(4), window=3), cases.delta_sizes(3, 1, 20, 12, 5), 0.0, 1.0), None),
-                                    (cases.parallel(cases.attn_sizes(1, 1, 16, cases.rot(4), window=3), cases.delta_sizes(2, 2, 128, 8, 2), 0.0, 1.0), None)])
-ONLY_WKV = cases.config(72, 101, [(cases.wkv(2, 36), None), (cases.wkv(5, 8), None), (cases.wkv(1, 128), None)])
+                                    (cases.parallel(cases.attn_sizes(1, 1, 16, cases.rot(4), window=3), cases.delta_sizes(2, 2, 128, 8, 2), 0.0, 1.0), None),
+                                    (cases.parallel(cases.attn_sizes(1, 1, 16, cases.rot(4), window=3), cases.delta_sizes(1, 1, 200, 136, 2), 0.0, 1.0), None)])
+ONLY_WKV = cases.config(72, 101, [(cases.wkv(2, 36), None), (cases.wkv(5, 8), None), (cases.wkv(1, 128), None), (cases.wkv(1, 160), None)])
 ONLY_ATTENTION = cases.config(72, 101, [(cases.attention(3, 1, 24, cases.rot(12, 3000.0, yarn=(4.0, 32, 8.0, 1.0)), window=11, softcap=3.0), None),
                                         (cases.parallel(cases.attn_sizes(2, 2, 8, cases.rot(8), window=40), cases.delta_sizes(1, 1, 4, 4, 1), 1.0, 0.0), None)])
 ONLY_FEED_FORWARD = cases.config(56, 89, [(cases.wkv(1, 4), 70)], logit_softcap=3.0)
