@@ -206,7 +206,9 @@ struct ScanArgs {
     // request * max_pieces + piece. Mode 1 runs every piece from a zero memory, writes no output, and leaves the piece's
     // memory in piece_s [z, H, D, DV] and the product of its decays in piece_p [z, H, D]; mode 2 runs every piece from
     // piece_s (by then the memory at the piece's start), writes the outputs and leaves the state alone.
-    int mode, piece, max_pieces;
+    // init (mode 1): 1 starts every column from zero, 2 from the unit matrix (column j holds a one in row j): with no values
+    // (v null) the memory of a piece then ends as the matrix that carries any memory across the piece.
+    int mode, piece, max_pieces, init;
     float* piece_s;
     float* piece_p;
 };
@@ -253,7 +255,8 @@ scan_kernel(const ScanArgs p) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int i = row_of(r), j = j0 + c * COLS;
-            S[c][r] = (p.mode != 1 && i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
+            S[c][r] = p.mode == 1 ? ((p.init == 2 && i == j && i < D) ? 1.f : 0.f)
+                                  : ((i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f);
         }
     float decayed[R];           // mode 1: the product of the decays of this thread's rows over the piece
 #pragma unroll
@@ -283,7 +286,7 @@ scan_kernel(const ScanArgs p) {
             const int idx = n * THREADS + threadIdx.x;
             const int tt = idx / CTA_COLS, c = idx - tt * CTA_COLS;
             const int col = blockIdx.x * CTA_COLS + c;
-            fv[n] = (tt < CHUNK && c0 + tt < len && col < DV)
+            fv[n] = (p.v != nullptr && tt < CHUNK && c0 + tt < len && col < DV)
                         ? load_any(p.v, static_cast<size_t>(start + c0 + tt) * p.ldv + h * DV + col, p.in_bf16) : 0.f;
         }
         if (RULE == 0 && threadIdx.x < CHUNK)
@@ -408,27 +411,30 @@ scan_kernel(const ScanArgs p) {
         if (more) stash(buf ^ 1);       // nobody reads that buffer: its chunk was finished before the last barrier
         __syncthreads();
     }
-    if (p.mode == 2) return;
+    if (p.mode != 2) {
 #pragma unroll
-    for (int c = 0; c < NC; ++c)
+        for (int c = 0; c < NC; ++c)
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int i = row_of(r), j = j0 + c * COLS;
-            if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[c][r];
-        }
+            for (int r = 0; r < R; ++r) {
+                const int i = row_of(r), j = j0 + c * COLS;
+                if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[c][r];
+            }
+    }
     if (p.mode == 1) {
-        if (blockIdx.x == 0 && jc == 0) {
+        if (RULE == 1 && blockIdx.x == 0 && jc == 0) {
 #pragma unroll
             for (int r = 0; r < R; ++r)
                 if (row_of(r) < D) p.piece_p[(static_cast<size_t>(blockIdx.z) * H + h) * D + row_of(r)] = decayed[r];
         }
         return;
     }
+    if (p.mode == 2 && first != 0) return;          // the CTAs of a request's first piece move the tail
     // The convolution's tail: row m of the new tail is the input of local token len - (taps - 1) + m, which lies in
     // this step or, for a short step, further up in the old tail. Channels are shared out over the CTAs of the request;
     // a channel's rows move in ascending order, so a row is read before it is overwritten.
     if (p.taps > 1) {
         const int keep = p.taps - 1;
+        const int len = p.q_len[seq];               // of the whole request, whatever this CTA's piece
         float* tail = p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride + p.tail_off;
         const int cta = blockIdx.y * gridDim.x + blockIdx.x, ctas = gridDim.x * gridDim.y;
         for (int c = cta * blockDim.x + threadIdx.x; c < p.C; c += ctas * blockDim.x)
@@ -467,6 +473,83 @@ pieces_combine_kernel(float* __restrict__ piece_s, const float* __restrict__ pie
         S = fmaf(piece_p[z * H * D + row], S, own);
     }
     *S_g = S;
+}
+
+// The same for the delta rule, whose pieces carry a memory across by a full matrix: piece_t [z, H, D, D] holds it, piece_s
+// [z, H, D, DV] what the piece adds from a zero memory; S_next = T S + B. A CTA owns 16 columns of S of one head of one
+// request and walks the pieces in order; T comes through shared memory in slabs of 16 columns. The memory at a piece's
+// start takes the place of the piece's own sum, the memory after the last piece goes into the state.
+constexpr int kCombineCols = 16, kCombineThreads = 256, kCombineMaxD = 256;
+
+__global__ void __launch_bounds__(kCombineThreads)
+delta_pieces_combine_kernel(float* __restrict__ piece_s, const float* __restrict__ piece_t, float* __restrict__ state,
+                            long long state_stride, const int32_t* __restrict__ q_len, const int32_t* __restrict__ state_slot, int H, int D,
+                            int DV, int piece, int max_pieces) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int PER = kCombineMaxD * kCombineCols / kCombineThreads;       // entries of the CTA's columns a thread, at most
+    __shared__ float S_s[kCombineMaxD][kCombineCols], T_s[kCombineMaxD][kCombineCols + 1];
+    const int seq = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * kCombineCols;
+    const int len = q_len[seq];
+    if (len <= 0) return;
+    float* S_g = state + static_cast<size_t>(state_slot[seq]) * state_stride + static_cast<size_t>(h) * D * DV;
+    const int entries = D * kCombineCols;
+    for (int idx = threadIdx.x; idx < entries; idx += kCombineThreads) {
+        const int row = idx / kCombineCols, col = idx % kCombineCols;
+        S_s[row][col] = c0 + col < DV ? S_g[static_cast<size_t>(row) * DV + c0 + col] : 0.f;
+    }
+    __syncthreads();
+    const int pieces = (len + piece - 1) / piece;
+    for (int c = 0; c < pieces; ++c) {
+        const size_t z = static_cast<size_t>(seq) * max_pieces + c;
+        const float* T = piece_t + (z * H + h) * D * D;
+        float* B = piece_s + (z * H + h) * D * DV;
+        float acc[PER];
+#pragma unroll
+        for (int n = 0; n < PER; ++n) acc[n] = 0.f;
+        for (int k0 = 0; k0 < D; k0 += kCombineCols) {
+            for (int idx = threadIdx.x; idx < entries; idx += kCombineThreads) {
+                const int row = idx / kCombineCols, kk = idx % kCombineCols;
+                T_s[row][kk] = k0 + kk < D ? T[static_cast<size_t>(row) * D + k0 + kk] : 0.f;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int n = 0; n < PER; ++n) {
+                const int idx = n * kCombineThreads + threadIdx.x;
+                if (idx < entries) {
+                    const int row = idx / kCombineCols, col = idx % kCombineCols;
+#pragma unroll
+                    for (int kk = 0; kk < kCombineCols; ++kk)
+                        if (k0 + kk < D) acc[n] = fmaf(T_s[row][kk], S_s[k0 + kk][col], acc[n]);
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int n = 0; n < PER; ++n) {
+            const int idx = n * kCombineThreads + threadIdx.x;
+            if (idx < entries) {
+                const int row = idx / kCombineCols, col = idx % kCombineCols;
+                if (c0 + col < DV) {
+                    float* at = B + static_cast<size_t>(row) * DV + c0 + col;
+                    const float own = *at;
+                    *at = S_s[row][col];                // every thread reads and writes its own entries only
+                    acc[n] += own;
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int n = 0; n < PER; ++n) {
+            const int idx = n * kCombineThreads + threadIdx.x;
+            if (idx < entries) S_s[idx / kCombineCols][idx % kCombineCols] = acc[n];
+        }
+        __syncthreads();
+    }
+    for (int idx = threadIdx.x; idx < entries; idx += kCombineThreads) {
+        const int row = idx / kCombineCols, col = idx % kCombineCols;
+        if (c0 + col < DV) S_g[static_cast<size_t>(row) * DV + c0 + col] = S_s[row][col];
+    }
 }
 
 template <int LANES, int R, int CHUNK, int RULE>
@@ -524,11 +607,16 @@ int stride_delta_prepare(const void* proj, int ld, const float* conv_w, const fl
 
 // The gated delta rule over the step's requests. qk, v, beta, decay: what delta_prepare wrote. proj: the projections
 // whose last taps - 1 rows become the convolution's new tail.
+// piece > 0: in pieces of that many tokens, parallel over the pieces (every piece from a zero memory; every piece's matrix;
+// the memories at the pieces' starts; every piece from its start). scratch: float32, at least
+// num_seqs * max_pieces * H * D * (DV + D). As for the other rule, the sums then take another order than the chain's.
 int stride_delta_scan(const float* qk, const float* v, const float* beta, const float* decay, float* o, float* state,
                       long long state_stride, long long tail_off, const void* proj, int ld_proj, const int32_t* q_start,
                       const int32_t* q_len, const int32_t* state_slot, int num_seqs, int G, int H, int D, int DV, int taps, int dtype,
-                      cudaStream_t stream) {
+                      int piece, int max_pieces, float* scratch, cudaStream_t stream) {
     if (num_seqs < 0 || G <= 0 || H <= 0 || D <= 0 || DV <= 0 || taps <= 0 || H % G) return STRIDE_BAD_ARGUMENT;
+    if (piece < 0 || (piece > 0 && (max_pieces <= 0 || scratch == nullptr))) return STRIDE_BAD_ARGUMENT;
+    if (piece > 0 && D > kCombineMaxD) return STRIDE_UNSUPPORTED;
     if (dtype != STRIDE_DTYPE_F32 && dtype != STRIDE_DTYPE_BF16) return STRIDE_BAD_ARGUMENT;
     if (num_seqs == 0) return 0;
     ScanArgs p = {};
@@ -556,7 +644,30 @@ int stride_delta_scan(const float* qk, const float* v, const float* beta, const 
     p.taps = taps;
     p.tail_off = tail_off;
     p.proj_bf16 = dtype == STRIDE_DTYPE_BF16 ? 1 : 0;      // the tail is read in the projections' type, the rest is float32
-    return launch_scan<0>(p, num_seqs, stream);
+    if (piece == 0) return launch_scan<0>(p, num_seqs, stream);
+    const size_t zs = static_cast<size_t>(num_seqs) * max_pieces;
+    float* piece_s = scratch;
+    float* piece_t = scratch + zs * H * D * DV;
+    p.piece = piece;
+    p.max_pieces = max_pieces;
+    p.mode = 1;
+    p.init = 1;
+    p.piece_s = piece_s;
+    int code = launch_scan<0>(p, num_seqs, stream);             // what every piece adds from a zero memory
+    if (code != 0) return code;
+    ScanArgs t = p;
+    t.v = nullptr;
+    t.DV = D;
+    t.init = 2;
+    t.piece_s = piece_t;
+    code = launch_scan<0>(t, num_seqs, stream);                 // every piece's matrix
+    if (code != 0) return code;
+    stride::launch(delta_pieces_combine_kernel, dim3((DV + kCombineCols - 1) / kCombineCols, H, num_seqs), dim3(kCombineThreads), 0, stream,
+                   piece_s, static_cast<const float*>(piece_t), state, state_stride, q_len, state_slot, H, D, DV, piece, max_pieces);
+    code = STRIDE_LAUNCH_STATUS();
+    if (code != 0) return code;
+    p.mode = 2;
+    return launch_scan<0>(p, num_seqs, stream);                 // every piece from its start, with the outputs
 }
 
 // Decayed memory with a bonus. r, k, v [tokens, H * D] in the compute type (one head size for keys and values);

@@ -121,7 +121,7 @@ _SIGNATURES = {
                                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "stride_delta_scan": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p,
                                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                c_void_p]),
+                                                c_int, c_int, c_void_p, c_void_p]),
     "stride_bonus_scan": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_shift_mix": ("linear_recurrence", [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -363,6 +363,12 @@ def tanh_(x) -> None:
 
 
 # ------------------------------------------------------------ matrix memories (delta rule, decayed memory with a bonus)
+MEMORY_PIECE = 64       # tokens a piece when a matrix memory runs its long portions in pieces
+# The delta rule in pieces is off by default (0): a piece needs its D x D matrix besides its own sum, three passes over the
+# tokens in all, and measured at 16 heads of 128 x 128 over 2,048 tokens that takes 1.94 ms against the chain's 0.91 ms.
+# STRIDE_B200_DELTA_PIECES_MIN=256 switches it on for portions of that many tokens.
+DELTA_PIECES_MIN_TOKENS = int(_os.environ.get("STRIDE_B200_DELTA_PIECES_MIN", "0"))
+
 def delta_prepare(proj, conv_w, low, a_log, dt_bias, state, tail_off: int, seq_of_token, q_start, state_slot, qk, v, beta, decay,
                   G: int, H: int, D: int, DV: int, taps: int, unit_eps: float) -> None:
     """Per token of the step, from ``proj`` [tokens, >= 2GD + HV + H] (q, k, v, beta's projection) and ``low`` (float32,
@@ -381,18 +387,24 @@ def delta_prepare(proj, conv_w, low, a_log, dt_bias, state, tail_off: int, seq_o
         _code(proj.dtype), _stream()), "delta_prepare")
 
 
+def delta_scan_scratch_floats(num_seqs: int, max_q_len: int, H: int, D: int, DV: int) -> int:
+    return num_seqs * -(-max_q_len // MEMORY_PIECE) * H * D * (DV + D)
+
+
 def delta_scan(qk, v, beta, decay, o, state, tail_off: int, proj, q_start, q_len, state_slot, num_seqs: int, G: int, H: int, D: int,
-               DV: int, taps: int) -> None:
+               DV: int, taps: int, max_q_len: int = 0, scratch=None) -> None:
     """The gated delta rule over every request of the step, in token order: ``o`` [tokens, H * DV] float32; S and the
-    convolution's tail in ``state`` move on."""
+    convolution's tail in ``state`` move on. With ``scratch`` (float32, ``delta_scan_scratch_floats`` for the step's longest
+    portion ``max_q_len``) the portions run in pieces of ``MEMORY_PIECE`` tokens, parallel over the pieces."""
+    piece = MEMORY_PIECE if scratch is not None else 0
+    max_pieces = -(-max_q_len // MEMORY_PIECE) if piece else 0
+    if piece and (max_pieces <= 0 or scratch.numel() < delta_scan_scratch_floats(num_seqs, max_q_len, H, D, DV)):
+        raise KernelError("delta_scan: the scratch is too small")
     _check(_fn("stride_delta_scan")(
         _dev(qk, "qk", torch.float32), _dev(v, "v", torch.float32), _dev(beta, "beta", torch.float32), _dev(decay, "decay", torch.float32),
         _dev(o, "o", torch.float32), _dev(state, "state", torch.float32), state.shape[1], int(tail_off), _dev(proj, "proj"), proj.shape[1],
         _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32), num_seqs,
-        G, H, D, DV, taps, _code(proj.dtype), _stream()), "delta_scan")
-
-
-MEMORY_PIECE = 64       # tokens a piece when a decayed memory runs its portions in pieces
+        G, H, D, DV, taps, _code(proj.dtype), piece, max_pieces, _opt(scratch, "scratch", torch.float32), _stream()), "delta_scan")
 
 
 def bonus_scan_scratch_floats(num_seqs: int, max_q_len: int, H: int, D: int) -> int:

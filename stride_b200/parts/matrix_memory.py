@@ -121,8 +121,13 @@ class GatedDeltaMixer(Mixer):
         ops.delta_prepare(proj, self.conv_w, two, self.a_log, self.dt_bias, state, self.s_floats, ctx.seq_of_token[:tokens], ctx.q_start,
                           ctx.state_slot, qk, v, beta, decay, self.G, self.H, self.D, self.DV, self.taps, self.unit_eps)
         o = self.rt.buffer("delta_o", tokens, self.HV, f32)
+        scratch = None
+        if x.dtype == torch.bfloat16 and 0 < ops.DELTA_PIECES_MIN_TOKENS <= ctx.max_q_len:
+            # a long portion in pieces, parallel over the pieces (off by default: slower than the chain at the sizes measured)
+            seqs = ctx.num_seqs
+            scratch = self.rt.scratch("delta_pieces", ops.delta_scan_scratch_floats(seqs, ctx.max_q_len, self.H, self.D, self.DV))
         ops.delta_scan(qk, v, beta, decay, o, state, self.s_floats, proj, ctx.q_start, ctx.q_len, ctx.state_slot, seqs, self.G, self.H,
-                       self.D, self.DV, self.taps)
+                       self.D, self.DV, self.taps, ctx.max_q_len, scratch)
         mixed = self.rt.buffer("delta_mixed", tokens, self.HV)
         ops.head_norm_gate(o, self.norm_w, False, two, "sigmoid", mixed, self.H, self.DV, self.norm_eps, gate_off=self.HD)
         if lazy_output:

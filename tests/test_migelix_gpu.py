@@ -379,9 +379,12 @@ def test_the_memory_in_pieces_gives_the_chain(gpu, tmp_models, monkeypatch):
     """bfloat16, portions long enough for the recurrence in pieces (and a batch of two of them with a short one between):
     against the plain chain, with portions that end inside pieces and a slot that is used again."""
     from stride_b200.csrc import ops
-    cfg = cases.config(64, 101, [(cases.wkv(3, 20), None), (cases.wkv(1, 64), 48), (cases.wkv(2, 128), None)])
+    cfg = cases.config(64, 101, [(cases.wkv(3, 20), None), (cases.wkv(1, 64), 48), (cases.wkv(2, 128), None),
+                                 (cases.parallel(cases.attn_sizes(2, 1, 16, cases.rot(8), window=19), cases.delta_sizes(3, 1, 20, 12, 3), 0.7, 1.0), None),
+                                 (cases.parallel(cases.attn_sizes(2, 1, 16, cases.rot(8), window=19), cases.delta_sizes(2, 2, 128, 72, 4), 0.5, 1.2), 48)])
     folder, requests, want = model_case(tmp_models, "pieces", cfg, "bfloat16", 31, [300, 70, 261])
     monkeypatch.setattr(ops, "SCAN_PIECES_MIN_TOKENS", 128)
+    monkeypatch.setattr(ops, "DELTA_PIECES_MIN_TOKENS", 128)
     together = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": [0, len(t) // 2, len(t) - 1]} for r, t in requests.items()],
                  "end": list(requests)}]
     replay(folder, "bfloat16", together, want, 16, 3, "three prompts in one step", min_ok=0.97)
