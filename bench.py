@@ -468,16 +468,16 @@ def compare_configs_migelix(size: dict, layers: int):
     """(Migelix config.json, Llama config.json) of one size."""
     left = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
             "mask": {"size": size["window"]},
-            "rot": {"base": 50000.0, "dims": size["dim"] // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 10000.0, "dims": size["dim"] // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     right = {"heads": size["delta_heads"], "kv_heads": size["delta_heads"], "dim": size["delta_dim"], "vdim": size["delta_dim"], "conv": 4,
              "decay_rank": size["decay_rank"], "gate_rank": size["gate_rank"]}
     attention = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
-                 "mask": {"size": size["window"]}, "softcap": 50.0, "rot": {"base": 1e6, "dims": size["dim"]}}
+                 "mask": {"size": size["window"]}, "softcap": 30.0, "rot": {"base": 500000.0, "dims": size["dim"]}}
     memory = {"heads": size["memory_heads"], "dim": size["memory_dim"], "decay_rank": size["decay_rank"]}
-    kinds = [("parallel", {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}), ("wkv", memory), ("attention", attention)]
+    kinds = [("parallel", {"left": left, "right": right, "left_scale": 0.7, "right_scale": 1.2}), ("wkv", memory), ("attention", attention)]
     mlp = {"kind": "dense", "ff": size["ff"]}
     entries = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": mlp} for i in range(layers)]
-    ours = {"architecture": "Migelix", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-5}, "logit_softcap": 15.0,
+    ours = {"architecture": "Migelix", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
             "layers": entries}
     llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "hidden_size": size["width"],
              "num_attention_heads": size["heads"], "num_key_value_heads": size["kv"], "head_dim": size["dim"],
