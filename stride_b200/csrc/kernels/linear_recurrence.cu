@@ -218,11 +218,13 @@ struct ScanArgs {
 // sets the pace of a prompt is the chain of dependent instructions a token costs a warp (shared-memory reads, the sums,
 // the shuffles), not the amount of arithmetic: the rows are spread over as many lanes as the head size allows, and the NC
 // columns of a thread are independent chains that fill one another's waits (they also share the reads of k, q and the decay).
-template <int LANES, int R, int NC, int CHUNK, int RULE>      // RULE 0: gated delta rule, 1: decayed memory with a bonus
+// PIECES false: the one chain only (mode 0), with nothing of the pieces' bookkeeping in its loop.
+template <int LANES, int R, int NC, int CHUNK, int RULE, bool PIECES>      // RULE 0: gated delta rule, 1: decayed memory with a bonus
 __global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const ScanArgs p) {
     pdl_trigger();
     pdl_wait();
+    const int mode = PIECES ? p.mode : 0;
     constexpr int DP = R * LANES;                           // rows with padding
     constexpr int THREADS = kScanThreads;
     constexpr int COLS = THREADS / LANES;                   // columns of one pass over the threads
@@ -235,16 +237,16 @@ scan_kernel(const ScanArgs p) {
     __shared__ __align__(16) float s_a[2][CHUNK][DP], s_k[2][CHUNK][DP], s_w[2][CHUNK][DP];
     __shared__ float s_v[2][CHUNK][CTA_COLS], s_beta[2][CHUNK];
     __shared__ __align__(16) float s_bonus[DP], s_w0[DP];
-    const int seq = p.mode ? blockIdx.z / p.max_pieces : blockIdx.z, h = blockIdx.y;
-    const int first = p.mode ? (blockIdx.z % p.max_pieces) * p.piece : 0;         // this CTA's tokens of the request: [first, len)
-    const int len = p.mode ? min(p.q_len[seq], first + p.piece) : p.q_len[seq];
+    const int seq = mode ? blockIdx.z / p.max_pieces : blockIdx.z, h = blockIdx.y;
+    const int first = mode ? (blockIdx.z % p.max_pieces) * p.piece : 0;         // this CTA's tokens of the request: [first, len)
+    const int len = mode ? min(p.q_len[seq], first + p.piece) : p.q_len[seq];
     if (len <= first) return;
     const int start = p.q_start[seq];
     const int il = threadIdx.x & (LANES - 1), jc = threadIdx.x / LANES;
     const int j0 = blockIdx.x * CTA_COLS + jc;              // this thread's columns: j0 + c * COLS
     const int D = p.D, DV = p.DV, H = p.H;
     const int hk = h / p.group;
-    float* S_g = p.mode ? p.piece_s + (static_cast<size_t>(blockIdx.z) * H + h) * D * DV
+    float* S_g = mode ? p.piece_s + (static_cast<size_t>(blockIdx.z) * H + h) * D * DV
                         : p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride + static_cast<size_t>(h) * D * DV;
     // lane il of a column's lanes holds rows 4 LANES g + 4 il + e (g < R / 4, e < 4) in S[.][4 g + e]: four neighbouring rows
     // are one 16-byte read of shared memory, and the lanes read consecutive 16 bytes
@@ -255,7 +257,7 @@ scan_kernel(const ScanArgs p) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int i = row_of(r), j = j0 + c * COLS;
-            S[c][r] = p.mode == 1 ? ((p.init == 2 && i == j && i < D) ? 1.f : 0.f)
+            S[c][r] = mode == 1 ? ((p.init == 2 && i == j && i < D) ? 1.f : 0.f)
                                   : ((i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f);
         }
     float decayed[R];           // mode 1: the product of the decays of this thread's rows over the piece
@@ -286,7 +288,7 @@ scan_kernel(const ScanArgs p) {
             const int idx = n * THREADS + threadIdx.x;
             const int tt = idx / CTA_COLS, c = idx - tt * CTA_COLS;
             const int col = blockIdx.x * CTA_COLS + c;
-            fv[n] = (p.v != nullptr && tt < CHUNK && c0 + tt < len && col < DV)
+            fv[n] = ((!PIECES || p.v != nullptr) && tt < CHUNK && c0 + tt < len && col < DV)
                         ? load_any(p.v, static_cast<size_t>(start + c0 + tt) * p.ldv + h * DV + col, p.in_bf16) : 0.f;
         }
         if (RULE == 0 && threadIdx.x < CHUNK)
@@ -382,7 +384,7 @@ scan_kernel(const ScanArgs p) {
                     const float4 w = w4[LANES * g], k = k4[LANES * g], rr = a4[LANES * g], b = b4[LANES * g];
                     const float wv[4] = {w.x, w.y, w.z, w.w}, kv4[4] = {k.x, k.y, k.z, k.w}, rv[4] = {rr.x, rr.y, rr.z, rr.w},
                                 bv[4] = {b.x, b.y, b.z, b.w};
-                    if (p.mode == 1) {
+                    if (mode == 1) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) decayed[4 * g + e] = fmaf(wv[e], decayed[4 * g + e], decayed[4 * g + e]);
                     }
@@ -402,7 +404,7 @@ scan_kernel(const ScanArgs p) {
             for (int o = 1; o < LANES; o <<= 1)
 #pragma unroll
                 for (int c = 0; c < NC; ++c) out[c] += __shfl_xor_sync(0xffffffffu, out[c], o);
-            if (il == 0 && p.mode != 1) {
+            if (il == 0 && mode != 1) {
 #pragma unroll
                 for (int c = 0; c < NC; ++c)
                     if (j0 + c * COLS < DV) p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j0 + c * COLS] = out[c];
@@ -411,7 +413,7 @@ scan_kernel(const ScanArgs p) {
         if (more) stash(buf ^ 1);       // nobody reads that buffer: its chunk was finished before the last barrier
         __syncthreads();
     }
-    if (p.mode != 2) {
+    if (mode != 2) {
 #pragma unroll
         for (int c = 0; c < NC; ++c)
 #pragma unroll
@@ -420,7 +422,7 @@ scan_kernel(const ScanArgs p) {
                 if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[c][r];
             }
     }
-    if (p.mode == 1) {
+    if (mode == 1) {
         if (RULE == 1 && blockIdx.x == 0 && jc == 0) {
 #pragma unroll
             for (int r = 0; r < R; ++r)
@@ -428,20 +430,20 @@ scan_kernel(const ScanArgs p) {
         }
         return;
     }
-    if (p.mode == 2 && first != 0) return;          // the CTAs of a request's first piece move the tail
+    if (mode == 2 && first != 0) return;          // the CTAs of a request's first piece move the tail
     // The convolution's tail: row m of the new tail is the input of local token len - (taps - 1) + m, which lies in
     // this step or, for a short step, further up in the old tail. Channels are shared out over the CTAs of the request;
     // a channel's rows move in ascending order, so a row is read before it is overwritten.
     if (p.taps > 1) {
         const int keep = p.taps - 1;
-        const int len = p.q_len[seq];               // of the whole request, whatever this CTA's piece
+        const int all = PIECES ? p.q_len[seq] : len;        // the whole request's tokens, whatever this CTA's piece
         float* tail = p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride + p.tail_off;
         const int cta = blockIdx.y * gridDim.x + blockIdx.x, ctas = gridDim.x * gridDim.y;
         for (int c = cta * blockDim.x + threadIdx.x; c < p.C; c += ctas * blockDim.x)
             for (int m = 0; m < keep; ++m) {
-                const int src = len - keep + m;
+                const int src = all - keep + m;
                 tail[static_cast<size_t>(m) * p.C + c] = src >= 0 ? load_any(p.proj, static_cast<size_t>(start + src) * p.ld_proj + c, p.proj_bf16)
-                                                                 : tail[static_cast<size_t>(m + len) * p.C + c];
+                                                                 : tail[static_cast<size_t>(m + all) * p.C + c];
             }
     }
 }
@@ -559,10 +561,12 @@ int launch_scan_as(const ScanArgs& p, int num_seqs, cudaStream_t stream) {
     if (p.mode) num_seqs *= p.max_pieces;
     if (p.DV >= 4 * COLS) {
         const dim3 grid((p.DV + 4 * COLS - 1) / (4 * COLS), p.H, num_seqs);
-        stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE>, grid, dim3(kScanThreads), 0, stream, p);
+        if (p.mode) stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE, true>, grid, dim3(kScanThreads), 0, stream, p);
+        else stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE, false>, grid, dim3(kScanThreads), 0, stream, p);
     } else {
         const dim3 grid((p.DV + COLS - 1) / COLS, p.H, num_seqs);
-        stride::launch(scan_kernel<LANES, R, 1, CHUNK, RULE>, grid, dim3(kScanThreads), 0, stream, p);
+        if (p.mode) stride::launch(scan_kernel<LANES, R, 1, CHUNK, RULE, true>, grid, dim3(kScanThreads), 0, stream, p);
+        else stride::launch(scan_kernel<LANES, R, 1, CHUNK, RULE, false>, grid, dim3(kScanThreads), 0, stream, p);
     }
     return STRIDE_LAUNCH_STATUS();
 }
