@@ -59,6 +59,20 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same without the attribute: the kernel starts when everything before it on the stream has ended, and what follows it
+// starts when it has ended. For a kernel that keeps few CTAs busy for long, where waiting neighbours only cost.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_alone(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // The same for a kernel whose CTAs form clusters of `cluster_z` along z (CTAs of a cluster run at the same time on
 // SMs of one GPC and can write into one another's shared memory).
 template <typename... KArgs, typename... Args>

@@ -222,8 +222,7 @@ struct ScanArgs {
 template <int LANES, int R, int NC, int CHUNK, int RULE, bool PIECES>      // RULE 0: gated delta rule, 1: decayed memory with a bonus
 __global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const ScanArgs p) {
-    pdl_trigger();
-    pdl_wait();
+    // Launched without programmatic dependent launch (launch_alone): no trigger, and nothing to wait for.
     const int mode = PIECES ? p.mode : 0;
     constexpr int DP = R * LANES;                           // rows with padding
     constexpr int THREADS = kScanThreads;
@@ -561,12 +560,12 @@ int launch_scan_as(const ScanArgs& p, int num_seqs, cudaStream_t stream) {
     if (p.mode) num_seqs *= p.max_pieces;
     if (p.DV >= 4 * COLS) {
         const dim3 grid((p.DV + 4 * COLS - 1) / (4 * COLS), p.H, num_seqs);
-        if (p.mode) stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE, true>, grid, dim3(kScanThreads), 0, stream, p);
-        else stride::launch(scan_kernel<LANES, R, 4, CHUNK, RULE, false>, grid, dim3(kScanThreads), 0, stream, p);
+        if (p.mode) stride::launch_alone(scan_kernel<LANES, R, 4, CHUNK, RULE, true>, grid, dim3(kScanThreads), 0, stream, p);
+        else stride::launch_alone(scan_kernel<LANES, R, 4, CHUNK, RULE, false>, grid, dim3(kScanThreads), 0, stream, p);
     } else {
         const dim3 grid((p.DV + COLS - 1) / COLS, p.H, num_seqs);
-        if (p.mode) stride::launch(scan_kernel<LANES, R, 1, CHUNK, RULE, true>, grid, dim3(kScanThreads), 0, stream, p);
-        else stride::launch(scan_kernel<LANES, R, 1, CHUNK, RULE, false>, grid, dim3(kScanThreads), 0, stream, p);
+        if (p.mode) stride::launch_alone(scan_kernel<LANES, R, 1, CHUNK, RULE, true>, grid, dim3(kScanThreads), 0, stream, p);
+        else stride::launch_alone(scan_kernel<LANES, R, 1, CHUNK, RULE, false>, grid, dim3(kScanThreads), 0, stream, p);
     }
     return STRIDE_LAUNCH_STATUS();
 }
